@@ -73,6 +73,22 @@ int tb_residual_norm_rows(float* x, int64_t ldx, const float* y, int64_t ldy, co
                           int w_dtype, float w_offset, float eps, float out_scale, void* h, int h_dtype, int64_t ldh, int rows,
                           int cols, tb_stream_t stream);
 
+/* Layer normalisation with weight and bias: out = (x - mean) / sqrt(var + eps) * w + b over `cols` columns of each fp32 row
+ * (row stride ldi), var = mean of the squared deviations; w, b of type w_dtype (b may be NULL); out in out_dtype.
+ * rows_idx != NULL: row r of out comes from row rows_idx[r] of x. */
+int tb_layernorm_rows(void* out, int out_dtype, int64_t ldo, const float* x, int64_t ldi, const void* w, const void* b, int w_dtype,
+                      float eps, const int* rows_idx, int rows, int cols, tb_stream_t stream);
+/* The residual step of a layer whose sublayers all read one normalised input and are summed, with the next layer's input, in
+ * one pass: x <- x + out_scale * (y1 + y2) (y2 may be NULL), then h = layer_norm(x; w, b) stored as h_dtype.  w == NULL: only
+ * the residual step.  Computes what the sum followed by tb_layernorm_rows computes. */
+int tb_residual_layernorm_rows(float* x, int64_t ldx, const float* y1, int64_t ldy1, const float* y2, int64_t ldy2, float out_scale,
+                               const void* w, const void* b, int w_dtype, float eps, void* h, int h_dtype, int64_t ldh, int rows,
+                               int cols, tb_stream_t stream);
+/* out[r] = [a[r, :cols_a] | b[r, :cols_b]] (fp32 inputs with row strides lda / ldb) in out_dtype, contiguous: the operand of a
+ * projection that reads two streams side by side. */
+int tb_concat_rows(void* out, int out_dtype, const float* a, int64_t lda, int cols_a, const float* b, int64_t ldb, int cols_b,
+                   int rows, tb_stream_t stream);
+
 /* x[r, :cols] += vec (fp32 rows with stride ld; vec fp32 or bf16): the vector a pass of a looped block of layers adds to
  * the residual stream. */
 int tb_add_row_vector(float* x, int64_t ld, const void* vec, int v_dtype, int rows, int cols, tb_stream_t stream);
@@ -181,6 +197,59 @@ int tb_window_attention(void* out, const void* q, const void* pool, int dtype, c
                         int max_blocks, int page, int rows, int heads, int kv_heads, int dim, int vdim, float scale,
                         int window, int mode, int nsplit, float* workspace, tb_stream_t stream);
 
+/* The same attention with value heads shared by neighbouring key heads: there are kv_heads key heads but only kv_heads / v_share
+ * value heads, key head g reads value head g / v_share, and a pool entry is [kv_heads][dim] keys, then [kv_heads / v_share][vdim]
+ * values (several attention maps over one set of values).  out_f32 != 0: the result is stored as fp32 [N, heads, vdim] whatever
+ * the storage type (for a step that combines maps before anything is rounded).  v_share = 1, out_f32 = 0 is
+ * tb_window_attention. */
+int tb_window_attention_shared_values(void* out, int out_f32, const void* q, const void* pool, int dtype, const float* gate,
+                                      int64_t ldg, const void* sink, int sink_dtype, const int* tok_seq, const int* tok_pos,
+                                      const int* block_table, const int* seq_start, const int* seq_len, const int* seq_past,
+                                      int seqs, int max_len, int max_blocks, int page, int rows, int heads, int kv_heads,
+                                      int v_share, int dim, int vdim, float scale, int window, int mode, int nsplit,
+                                      float* workspace, tb_stream_t stream);
+
+/* ---- differential attention: two attention maps per head over one set of values ---------------------------------------
+ * tb_qk_norm_append: proj fp32 [N, ldp] holds per row q_vectors query vectors, k_vectors key vectors (each of `dim`) and
+ * v_channels value channels.  Every query and key vector is RMS-normalised over dim (x / sqrt(mean(x^2) + eps)) and multiplied
+ * by wq / wk ([dim], shared by all vectors; NULL: none); queries are also multiplied by the position's temperature
+ * 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1) (temp_every <= 0: none).  Queries go to q_out T [N, q_vectors, dim]; keys
+ * and values to the row's position in its pages (entry = [k_vectors][dim] keys, then v_channels values). */
+int tb_qk_norm_append(void* q_out, void* pool, int dtype, const float* proj, int64_t ldp, const void* wq, const void* wk, int w_dtype,
+                      float eps, float temp_coef, int temp_every, const int* tok_seq, const int* tok_pos, const int* block_table,
+                      int max_blocks, int page, int rows, int q_vectors, int k_vectors, int dim, int v_channels, tb_stream_t stream);
+/* maps fp32 [N, kv_heads, 2, per, vdim]: for every key/value head the first and the second map of its `per` query heads.
+ * out T [N, kv_heads * per, vdim] = o / sqrt(mean(o^2) + eps) * mult with o = map1 - lambda * map2 and
+ * lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff (the four vectors of ldim elements, type w_dtype).  All fp32. */
+int tb_diff_combine(void* out, int dtype, const float* maps, const void* lq1, const void* lk1, const void* lq2, const void* lk2,
+                    int w_dtype, int ldim, float diff, float eps, float mult, int rows, int kv_heads, int per, int vdim,
+                    tb_stream_t stream);
+
+/* ---- gated delta rule -----------------------------------------------------------------------------------------------------
+ * Per head a state S [dim, vdim] (fp32): S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  `heads` value heads,
+ * `kv_heads` query / key heads (head h uses query / key head h / (heads / kv_heads)).
+ *
+ * tb_delta_prepare: proj fp32 [N, ldp]; its first C = 2 kv_heads dim + heads vdim columns are q | k | v.  Each of these channels
+ * runs a causal convolution of `taps` taps (conv_w [C, taps], no bias; the last tap weighs the current input) over the row's portion
+ * and the carried inputs state[slot] (fp32 [slots, taps - 1, C], oldest first; zeros before the sequence's start), then SiLU.
+ * Queries and keys are then divided by sqrt(sum(x^2) + eps_unit) per head, queries also by sqrt(dim).  u fp32 [N, C] receives
+ * q | k | v.  bg fp32 [N, 2 heads] receives beta = sigmoid(proj[col_b + h]) and g = exp(-exp(a_log[h]) * softplus(proj[col_a + h]
+ * + dt_bias[h])).  state_rw == state: a sequence that brings ONE row has its carried inputs moved on here; run
+ * tb_causal_conv1d_update(state, proj, ldp, ..., C, taps, 1) afterwards for the others. */
+int tb_delta_prepare(float* u, float* bg, const float* proj, int64_t ldp, const void* conv_w, const void* a_log, const void* dt_bias,
+                     int w_dtype, int col_b, int col_a, const float* state, float* state_rw, const int* tok_seq, const int* tok_pos,
+                     const int* seq_start, const int* seq_len, const int* seq_past, const int* seq_slot, int rows, int heads,
+                     int kv_heads, int dim, int vdim, int taps, float eps_unit, tb_stream_t stream);
+/* The recurrence over every sequence's rows in order, from state[slot] (fp32 [slots, heads, vdim, dim]: S transposed, a value
+ * column's elements contiguous; zeros at a sequence's first position) and back into it.  out fp32 [N, heads, vdim].  dim <= 512. */
+int tb_delta_rule_scan(float* out, const float* u, const float* bg, float* state, const int* seq_start, const int* seq_len,
+                       const int* seq_past, const int* seq_slot, int seqs, int heads, int kv_heads, int dim, int vdim,
+                       tb_stream_t stream);
+/* out T [N, heads, vdim] = o / sqrt(mean_vdim(o^2) + eps) * w * silu(gate): o fp32 [N, heads, vdim]; w [vdim] shared by the heads
+ * (NULL: none); gate fp32 logits [N, >= heads * vdim] with row stride ldg (NULL: none). */
+int tb_gated_rmsnorm_heads(void* out, int dtype, const float* o, const float* gate, int64_t ldg, const void* w, int w_dtype, float eps,
+                           int rows, int heads, int vdim, tb_stream_t stream);
+
 /* ---- routed-expert feed-forward ------------------------------------------------------------------------------------
  * tb_moe_route: logits fp32 [N, experts].  s = sigmoid(logit); choice = s + correction (fp32 or bf16 [experts], NULL:
  * none).  Experts form `groups` equal groups of neighbours; a group scores the sum of its two largest choices and only the
@@ -188,6 +257,10 @@ int tb_window_attention(void* out, const void* q, const void* pool, int dtype, c
  * ids int32 [N, top], weights fp32 [N, top] = s of the chosen experts (not renormalised). */
 int tb_moe_route(int* ids, float* weights, const float* logits, const void* correction, int c_dtype, int rows, int experts,
                  int top, int groups, int keep, tb_stream_t stream);
+/* Softmax router: s = softmax(logits) over all experts (fp32); the `top` largest s are taken (ties: lower index);
+ * weights = s / (sum of the chosen s + 1e-20) * scale when renorm != 0, else s * scale. */
+int tb_moe_route_softmax(int* ids, float* weights, const float* logits, int rows, int experts, int top, int renorm, float scale,
+                         tb_stream_t stream);
 /* Plan: the N * top (token, choice) pairs sorted by expert, every expert's range padded to whole tiles of `tile` rows.
  * tb_moe_plan_tiles = the number of tiles that is always enough; slot_pair int32 [max_tiles * tile] (pair index, -1 in
  * the padding), tile_expert int32 [max_tiles] (-1: unused tile), pair_slot int32 [pairs] (the inverse map; may be NULL). */
@@ -219,6 +292,10 @@ int tb_moe_gemv(void* c, int c_dtype, int64_t ldc, const void* a, int a_dtype, i
  * plan order) or p itself when pair_slot is NULL (y fp32 in pair order). */
 int tb_moe_combine(float* out, const float* y, const float* weights, const int* pair_slot, int rows, int width, int top,
                    tb_stream_t stream);
+
+/* tb_moe_combine plus a term every token has: out = add + sum_k ... (add fp32 [N, width], e.g. a shared expert's output; NULL: none). */
+int tb_moe_combine_add(float* out, const float* y, const float* weights, const int* pair_slot, const float* add, int rows, int width,
+                       int top, tb_stream_t stream);
 
 #ifdef __cplusplus
 }

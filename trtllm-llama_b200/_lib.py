@@ -213,6 +213,19 @@ RAGGED_SIGNATURES = {
     "tb_moe_gemv": (i32, [vp, i32, i64, vp, i32, i64, vp, i32, vp, i32, i32, i32, i32, i32, f32, f32, vp]),
     "tb_moe_linear": (i32, [vp, i32, i64, vp, i32, i64, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]),
     "tb_moe_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
+    "tb_moe_combine_add": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, vp]),
+    "tb_moe_route_softmax": (i32, [vp, vp, vp, i32, i32, i32, i32, f32, vp]),
+    "tb_layernorm_rows": (i32, [vp, i32, i64, vp, i64, vp, vp, i32, f32, vp, i32, i32, vp]),
+    "tb_residual_layernorm_rows": (i32, [vp, i64, vp, i64, vp, i64, f32, vp, vp, i32, f32, vp, i32, i64, i32, i32, vp]),
+    "tb_concat_rows": (i32, [vp, i32, vp, i64, i32, vp, i64, i32, i32, vp]),
+    "tb_window_attention_shared_values": (i32, [vp, i32, vp, vp, i32, vp, i64, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
+                                                i32, i32, i32, i32, i32, i32, f32, i32, i32, i32, vp, vp]),
+    "tb_qk_norm_append": (i32, [vp, vp, i32, vp, i64, vp, vp, i32, f32, f32, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]),
+    "tb_diff_combine": (i32, [vp, i32, vp, vp, vp, vp, vp, i32, i32, f32, f32, f32, i32, i32, i32, i32, vp]),
+    "tb_delta_prepare": (i32, [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
+                               i32, f32, vp]),
+    "tb_delta_rule_scan": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
+    "tb_gated_rmsnorm_heads": (i32, [vp, i32, vp, vp, i64, vp, i32, f32, i32, i32, i32, vp]),
 }
 SIGNATURES.update(RAGGED_SIGNATURES)
 # what libtrtllm_b200_ragged.so exports (csrc/Makefile target `ragged`): the operators above plus the sampling, arg-max
@@ -275,7 +288,7 @@ def load_ragged_library(build: bool = False):
     """The library that holds the ragged-batch operators: the full library when it is built (it contains them), else the
     subset library.  With ``build`` (the command-line tools pass it) a library whose sources changed since it was built is
     not trusted: the full one is used only if ``make`` calls it up to date, and the subset is (re)compiled on demand — a
-    fresh checkout that only serves such a model compiles eleven files and nothing else."""
+    fresh checkout that only serves such a model compiles thirteen files and nothing else."""
     global _ragged
     if _ragged is not None:
         return _ragged

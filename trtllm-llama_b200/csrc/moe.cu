@@ -7,6 +7,7 @@
 //                       groups of neighbours, a group scores the sum of its two largest choices, only the `keep` best
 //                       groups stay eligible; the `top` largest eligible choices are taken (ties: the lower index), and
 //                       their weights are the plain s, not renormalised.  All fp32.
+//   moe_route_softmax_kernel  one warp per token: s = softmax over all experts, the `top` largest, weights s / sum(chosen) * scale.
 //   moe_plan_kernel     one CTA: pairs counted per expert, every expert's range padded to whole tiles of `tile` rows
 //                       (so a tile never mixes experts), tile -> expert table, and sorted slot -> pair index (-1 in the
 //                       padding).  Everything stays on the device: a replayed step graph re-plans with the same launch.
@@ -101,6 +102,50 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(int* ids, f
   }
 }
 
+// Softmax router: s = softmax(logits) over ALL experts, the `top` largest are taken (ties: the lower index) and weighted by
+// s / (sum of the chosen s + 1e-20) * scale (renorm) or s * scale.  One warp per token; shared memory per warp: s [E] | taken [E].
+__global__ void __launch_bounds__(kRouteWarps * 32) moe_route_softmax_kernel(int* ids, float* weights, const float* logits, int rows,
+                                                                             int E, int top, int renorm, float scale) {
+  extern __shared__ float smem[];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int row = blockIdx.x * kRouteWarps + warp;
+  if (row >= rows) return;
+  float* sc = smem + (size_t) warp * 2 * E;
+  int* taken = reinterpret_cast<int*>(sc + E);
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, logits[(int64_t) row * E + e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float p = expf(logits[(int64_t) row * E + e] - mx);
+    sc[e] = p;
+    taken[e] = 0;
+    sum += p;
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) sc[e] = sc[e] / sum;
+  __syncwarp();
+  float chosen = 0.f;                                   // sum of the chosen scores, in choice order (the same on every lane)
+  for (int k = 0; k < top; ++k) {
+    float bv = -INFINITY; int bi = -1;
+    for (int e = lane; e < E; e += 32)
+      if (!taken[e] && (bi < 0 || sc[e] > bv)) { bv = sc[e]; bi = e; }
+    warp_argmax(bv, bi);
+    if (lane == 0) {
+      ids[(int64_t) row * top + k] = bi < 0 ? 0 : bi;
+      if (bi >= 0) taken[bi] = 1;
+    }
+    chosen += bi < 0 ? 0.f : bv;
+    __syncwarp();
+  }
+  __syncwarp();
+  for (int k = lane; k < top; k += 32) {
+    const float v = sc[ids[(int64_t) row * top + k]];
+    weights[(int64_t) row * top + k] = renorm ? v / (chosen + 1e-20f) * scale : v * scale;
+  }
+}
+
 // one CTA of 1024 threads; shared: count [E] | cursor [E]
 __global__ void __launch_bounds__(1024) moe_plan_kernel(int* slot_pair, int* tile_expert, int* pair_slot, const int* ids, int pairs,
                                                         int E, int tile, int max_tiles) {
@@ -140,8 +185,8 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(int* slot_pair, int* til
   }
 }
 
-__global__ void moe_combine_kernel(float* out, const float* y, const float* weights, const int* pair_slot, int64_t n, int width,
-                                   int top) {
+__global__ void moe_combine_kernel(float* out, const float* y, const float* weights, const int* pair_slot, const float* add,
+                                   int64_t n, int width, int top) {
   for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
     const int64_t row = i / width;
     const int c = (int) (i % width);
@@ -150,7 +195,7 @@ __global__ void moe_combine_kernel(float* out, const float* y, const float* weig
       const int64_t r = pair_slot ? pair_slot[row * top + k] : row * top + k;
       if (r >= 0) acc = fmaf(weights[row * top + k], y[r * width + c], acc);
     }
-    out[i] = acc;
+    out[i] = add ? acc + add[i] : acc;
   }
 }
 
@@ -192,6 +237,18 @@ extern "C" int tb_moe_route(int* ids, float* weights, const float* logits, const
   return 0;
 }
 
+extern "C" int tb_moe_route_softmax(int* ids, float* weights, const float* logits, int rows, int experts, int top, int renorm,
+                                    float scale, tb_stream_t stream) {
+  if (!ids || !weights || !logits || rows < 0 || experts <= 0 || top <= 0 || top > experts) return -1;
+  const size_t smem = (size_t) kRouteWarps * 2 * experts * sizeof(float);
+  if (smem > 48 * 1024) return -2;
+  if (rows == 0) return 0;
+  moe_route_softmax_kernel<<<(rows + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, (cudaStream_t) stream>>>(
+      ids, weights, logits, rows, experts, top, renorm, scale);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 extern "C" int tb_moe_plan_tiles(int pairs, int experts, int tile) {
   if (pairs < 0 || experts <= 0 || tile <= 0) return -1;
   const int full = (pairs + tile - 1) / tile;
@@ -225,11 +282,16 @@ extern "C" int tb_moe_gather_rows(void* xs, const void* x, int x_dtype, int64_t 
 
 extern "C" int tb_moe_combine(float* out, const float* y, const float* weights, const int* pair_slot, int rows, int width, int top,
                               tb_stream_t stream) {
+  return tb_moe_combine_add(out, y, weights, pair_slot, nullptr, rows, width, top, stream);
+}
+
+extern "C" int tb_moe_combine_add(float* out, const float* y, const float* weights, const int* pair_slot, const float* add, int rows,
+                                  int width, int top, tb_stream_t stream) {
   if (!out || !y || !weights || rows < 0 || width <= 0 || top <= 0) return -1;
   if (rows == 0) return 0;
   const int64_t n = (int64_t) rows * width;
   const int grid = (int) ((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-  moe_combine_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(out, y, weights, pair_slot, n, width, top);
+  moe_combine_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(out, y, weights, pair_slot, add, n, width, top);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

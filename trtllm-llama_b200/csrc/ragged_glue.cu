@@ -1,6 +1,6 @@
 // Row-wise kernels of the ragged-batch models whose residual stream is fp32: scaled embedding, RMS normalisation of a
-// sublayer's output accumulated into the residual, the clamped gated activation of the feed-forward, and the rotary
-// table.  All are bandwidth-bound passes over [rows, width]; statistics and sums are fp32.
+// sublayer's output accumulated into the residual, layer normalisation (alone and with the residual step of a layer whose
+// sublayers run side by side), the clamped gated activation of the feed-forward, and the rotary table.  All are bandwidth-bound passes over [rows, width]; statistics and sums are fp32.
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -95,6 +95,86 @@ __global__ void __launch_bounds__(256) residual_norm_rows_kernel(float* x, int64
   const float inv_x = block_inv(ss);
   for (int c = threadIdx.x; c < cols; c += 256)
     st_f(h, h_dtype, (int64_t) row * ldh + c, xr[c] * inv_x * (ld_f(w_pre, w_dtype, c) + w_offset));
+}
+
+// Layer normalisation of fp32 rows with weight and bias: (x - mean) / sqrt(var + eps) * w + b, var = mean of the squared
+// deviations (second pass over the row, not E[x^2] - mean^2).  Block sums run in a fixed tree.
+__device__ __forceinline__ float block_sum_256(float v, float* red, float* bcast) {
+  v = warp_sum(v);
+  __syncthreads();                                 // red / bcast of the previous reduction have been read
+  if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = v;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < 8 ? red[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) *bcast = t;
+  }
+  __syncthreads();
+  return *bcast;
+}
+
+__global__ void __launch_bounds__(256) layernorm_rows_kernel(void* out, int out_dtype, int64_t ldo, const float* x, int64_t ldi,
+                                                             const void* w, const void* b, int w_dtype, float eps,
+                                                             const int* rows_idx, int cols) {
+  __shared__ float red[8];
+  __shared__ float bc;
+  const int row = blockIdx.x;
+  const float* xr = x + (int64_t) (rows_idx ? rows_idx[row] : row) * ldi;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 256) s += xr[c];
+  const float mean = block_sum_256(s, red, &bc) / (float) cols;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 256) { const float d = xr[c] - mean; ss = fmaf(d, d, ss); }
+  const float inv = 1.f / sqrtf(block_sum_256(ss, red, &bc) / (float) cols + eps);
+  for (int c = threadIdx.x; c < cols; c += 256) {
+    float y = (xr[c] - mean) * inv * ld_f(w, w_dtype, c);
+    if (b) y += ld_f(b, w_dtype, c);
+    st_f(out, out_dtype, (int64_t) row * ldo + c, y);
+  }
+}
+
+// Residual step of a layer whose sublayers all read ONE normalised input and are added together, with the next layer's
+// input in the same pass: x <- x + out_scale * (y1 + y2);  h = layer_norm(x) (skipped when w is NULL).
+// A thread re-reads only what it wrote itself, so the row needs no fence between the passes.
+__global__ void __launch_bounds__(256) residual_layernorm_rows_kernel(float* x, int64_t ldx, const float* y1, int64_t ldy1,
+                                                                      const float* y2, int64_t ldy2, float out_scale, const void* w,
+                                                                      const void* b, int w_dtype, float eps, void* h, int h_dtype,
+                                                                      int64_t ldh, int cols) {
+  __shared__ float red[8];
+  __shared__ float bc;
+  const int row = blockIdx.x;
+  float* xr = x + (int64_t) row * ldx;
+  const float* ar = y1 + (int64_t) row * ldy1;
+  const float* br = y2 ? y2 + (int64_t) row * ldy2 : nullptr;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 256) {
+    float y = ar[c];
+    if (br) y += br[c];
+    const float v = fmaf(out_scale, y, xr[c]);
+    xr[c] = v;
+    s += v;
+  }
+  if (!w) return;
+  const float mean = block_sum_256(s, red, &bc) / (float) cols;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 256) { const float d = xr[c] - mean; ss = fmaf(d, d, ss); }
+  const float inv = 1.f / sqrtf(block_sum_256(ss, red, &bc) / (float) cols + eps);
+  for (int c = threadIdx.x; c < cols; c += 256) {
+    float y = (xr[c] - mean) * inv * ld_f(w, w_dtype, c);
+    if (b) y += ld_f(b, w_dtype, c);
+    st_f(h, h_dtype, (int64_t) row * ldh + c, y);
+  }
+}
+
+// out[r] = [a[r, :cols_a] | b[r, :cols_b]] in out's type: the operand of a projection that reads two fp32 streams side by side
+__global__ void concat_rows_kernel(void* out, int out_dtype, const float* a, int64_t lda, int cols_a, const float* b, int64_t ldb,
+                                   int cols_b, int64_t n) {
+  const int cols = cols_a + cols_b;
+  for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
+    const int64_t r = i / cols;
+    const int c = (int) (i % cols);
+    st_f(out, out_dtype, i, c < cols_a ? a[r * lda + c] : b[r * ldb + c - cols_a]);
+  }
 }
 
 __global__ void gated_act_kernel(void* out, int out_dtype, const float* gu, int64_t n, int ff, float alpha, float limit,
@@ -206,6 +286,38 @@ extern "C" int tb_residual_norm_rows(float* x, int64_t ldx, const float* y, int6
   if (rows == 0) return 0;
   residual_norm_rows_kernel<<<rows, 256, 0, (cudaStream_t) stream>>>(x, ldx, y, ldy, w_post, w_pre, w_dtype, w_offset, eps,
                                                                      out_scale, h, h_dtype, ldh, cols);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_layernorm_rows(void* out, int out_dtype, int64_t ldo, const float* x, int64_t ldi, const void* w, const void* b,
+                                 int w_dtype, float eps, const int* rows_idx, int rows, int cols, tb_stream_t stream) {
+  if (!out || !x || !w || !dt_ok(out_dtype) || !dt_ok(w_dtype) || cols <= 0 || rows < 0) return -1;
+  if (rows == 0) return 0;
+  layernorm_rows_kernel<<<rows, 256, 0, (cudaStream_t) stream>>>(out, out_dtype, ldo, x, ldi, w, b, w_dtype, eps, rows_idx, cols);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_residual_layernorm_rows(float* x, int64_t ldx, const float* y1, int64_t ldy1, const float* y2, int64_t ldy2,
+                                          float out_scale, const void* w, const void* b, int w_dtype, float eps, void* h, int h_dtype,
+                                          int64_t ldh, int rows, int cols, tb_stream_t stream) {
+  if (!x || !y1 || cols <= 0 || rows < 0) return -1;
+  if (w && (!h || !dt_ok(w_dtype) || !dt_ok(h_dtype))) return -1;
+  if (rows == 0) return 0;
+  residual_layernorm_rows_kernel<<<rows, 256, 0, (cudaStream_t) stream>>>(x, ldx, y1, ldy1, y2, ldy2, out_scale, w, b, w_dtype, eps,
+                                                                          h, h_dtype, ldh, cols);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_concat_rows(void* out, int out_dtype, const float* a, int64_t lda, int cols_a, const float* b, int64_t ldb,
+                              int cols_b, int rows, tb_stream_t stream) {
+  if (!out || !a || !b || !dt_ok(out_dtype) || cols_a <= 0 || cols_b <= 0 || rows < 0) return -1;
+  if (rows == 0) return 0;
+  const int64_t n = (int64_t) rows * (cols_a + cols_b);
+  const int grid = (int) ((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  concat_rows_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(out, out_dtype, a, lda, cols_a, b, ldb, cols_b, n);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -123,13 +123,15 @@ struct AttnArgs {
   const int *tok_seq, *tok_pos, *block_table;
   int max_blocks, page, H, G, dim, vdim, window;
   float scale;
+  int vsh, GV;                             // key heads per value head (key head g reads value head g / vsh), GV = G / vsh value heads
+  int out_f32;                             // the result is stored as fp32 whatever the storage type
 };
 
 // shared memory (fp32): keys [32][dim + 1] | values [32][vdim] | per warp q [dim]
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(T* out, const T* q, const T* pool, AttnArgs a) {
   extern __shared__ float smem[];
-  const int LDK = a.dim + 1, E = a.G * (a.dim + a.vdim), per = a.H / a.G;
+  const int LDK = a.dim + 1, E = a.G * a.dim + a.GV * a.vdim, per = a.H / a.G;
   float* keys = smem;
   float* vals = keys + kTile * LDK;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -162,7 +164,7 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(T* out, c
       const int jj = e / a.vdim, d = e % a.vdim, j = j0 + jj;
       float v = 0.f;
       if (j >= lo && j <= pos)
-        v = to_f<T>(pool[((int64_t) bt[j / a.page] * a.page + j % a.page) * E + a.G * a.dim + g * a.vdim + d]);
+        v = to_f<T>(pool[((int64_t) bt[j / a.page] * a.page + j % a.page) * E + a.G * a.dim + (g / a.vsh) * a.vdim + d]);
       vals[jj * a.vdim + d] = v;
     }
     __syncthreads();
@@ -191,11 +193,13 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(T* out, c
   if (live) {
     float f = 1.f / l;
     if (a.gate) f *= 1.f / (1.f + expf(-a.gate[(int64_t) row * a.ldg + head]));
-    T* dst = out + ((int64_t) row * a.H + head) * a.vdim;
+    const int64_t dst = ((int64_t) row * a.H + head) * a.vdim;
 #pragma unroll
     for (int c = 0; c < kMaxVPerLane; ++c) {
       const int col = c * 32 + lane;
-      if (col < a.vdim) dst[col] = from_f<T>(acc[c] * f);
+      if (col >= a.vdim) continue;
+      if (a.out_f32) reinterpret_cast<float*>(out)[dst + col] = acc[c] * f;
+      else out[dst + col] = from_f<T>(acc[c] * f);
     }
   }
 }
@@ -280,7 +284,7 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
   const int p_last = past + t_last;                     // last position any row of the CTA sees
   const int p_first = past + t_first;
   const int lo_cta = a.window > 0 && p_first - a.window + 1 > 0 ? p_first - a.window + 1 : 0;
-  const int E = a.G * (DIM + VDIM);
+  const int E = a.G * DIM + a.GV * VDIM;
   const int* bt = a.block_table + (int64_t) e * a.max_blocks;
 
   // queries of the CTA's rows (zeros for rows past the sequence's portion)
@@ -309,7 +313,7 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
     for (int i = threadIdx.x; i < kMmaKeys * (VDIM / 8); i += 128) {
       const int jj = i / (VDIM / 8), c = (i % (VDIM / 8)) * 8;
       const int64_t r = key_row[stage][jj];
-      cp_async16(vd + jj * LDV + c, r >= 0 ? pool + r + a.G * DIM + g * VDIM + c : pool, r >= 0);
+      cp_async16(vd + jj * LDV + c, r >= 0 ? pool + r + a.G * DIM + (g / a.vsh) * VDIM + c : pool, r >= 0);
     }
   };
   const int kt0 = lo_cta / kMmaKeys + split, kt1 = p_last / kMmaKeys;
@@ -459,10 +463,16 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
     const int R = r0 + warp * 16 + gq + h * 8, t = R / per;
     float f = 1.f / l_r[h];
     if (a.gate) f *= 1.f / (1.f + expf(-a.gate[(int64_t) (row0 + t) * a.ldg + head_r[h]]));
-    __nv_bfloat16* dst = out + ((int64_t) (row0 + t) * a.H + head_r[h]) * VDIM;
+    const int64_t dst = ((int64_t) (row0 + t) * a.H + head_r[h]) * VDIM;
+    if (a.out_f32) {
 #pragma unroll
-    for (int n = 0; n < VDIM / 8; ++n)
-      *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + 2 * tq) = __floats2bfloat162_rn(o[n][2 * h] * f, o[n][2 * h + 1] * f);
+      for (int n = 0; n < VDIM / 8; ++n)
+        *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + dst + n * 8 + 2 * tq) = make_float2(o[n][2 * h] * f, o[n][2 * h + 1] * f);
+    } else {
+#pragma unroll
+      for (int n = 0; n < VDIM / 8; ++n)
+        *reinterpret_cast<__nv_bfloat162*>(out + dst + n * 8 + 2 * tq) = __floats2bfloat162_rn(o[n][2 * h] * f, o[n][2 * h + 1] * f);
+    }
   }
 }
 
@@ -492,7 +502,9 @@ __global__ void window_attention_merge_kernel(__nv_bfloat16* out, const float* p
   for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < nsplit; ++s) acc = fmaf(src[s * (vdim + 2) + 2 + c], w_s[s], acc);
-    out[((int64_t) row * a.H + head) * vdim + c] = __float2bfloat16_rn(acc * f_s);
+    const int64_t o = ((int64_t) row * a.H + head) * vdim + c;
+    if (a.out_f32) reinterpret_cast<float*>(out)[o] = acc * f_s;
+    else out[o] = __float2bfloat16_rn(acc * f_s);
   }
 }
 
@@ -559,7 +571,20 @@ extern "C" int tb_window_attention(void* out, const void* q, const void* pool, i
                                    int seqs, int max_len, int max_blocks, int page, int rows, int heads, int kv_heads,
                                    int dim, int vdim, float scale, int window, int mode, int nsplit, float* workspace,
                                    tb_stream_t stream) {
+  return tb_window_attention_shared_values(out, 0, q, pool, dtype, gate, ldg, sink, sink_dtype, tok_seq, tok_pos, block_table,
+                                           seq_start, seq_len, seq_past, seqs, max_len, max_blocks, page, rows, heads, kv_heads, 1,
+                                           dim, vdim, scale, window, mode, nsplit, workspace, stream);
+}
+
+extern "C" int tb_window_attention_shared_values(void* out, int out_f32, const void* q, const void* pool, int dtype,
+                                                 const float* gate, int64_t ldg, const void* sink, int sink_dtype,
+                                                 const int* tok_seq, const int* tok_pos, const int* block_table,
+                                                 const int* seq_start, const int* seq_len, const int* seq_past, int seqs,
+                                                 int max_len, int max_blocks, int page, int rows, int heads, int kv_heads,
+                                                 int v_share, int dim, int vdim, float scale, int window, int mode, int nsplit,
+                                                 float* workspace, tb_stream_t stream) {
   if (!out || !q || !pool || !tok_seq || !tok_pos || !block_table) return -1;
+  if (v_share <= 0 || kv_heads % v_share) return -1;
   if (dtype != TB_DT_F32 && dtype != TB_DT_BF16) return -1;
   if (sink && sink_dtype != TB_DT_F32 && sink_dtype != TB_DT_BF16) return -1;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 || vdim > 32 * kMaxVPerLane || page <= 0 ||
@@ -567,7 +592,7 @@ extern "C" int tb_window_attention(void* out, const void* q, const void* pool, i
     return -1;
   if (rows == 0) return 0;
   AttnArgs a{gate, ldg, sink, sink_dtype, tok_seq, tok_pos, block_table, max_blocks, page, heads, kv_heads, dim, vdim,
-             window, scale};
+             window, scale, v_share, kv_heads / v_share, out_f32 ? 1 : 0};
   cudaStream_t s = (cudaStream_t) stream;
   if (mode == 0 && seq_start && seq_len && seq_past && seqs > 0 && max_len > 0 && seqs <= 65535 &&
       tb_window_attention_tensor_cores(dtype, heads, kv_heads, dim, vdim) && (uintptr_t) q % 16 == 0 && (uintptr_t) pool % 16 == 0) {

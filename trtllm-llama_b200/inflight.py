@@ -129,8 +129,8 @@ class InflightSession:
         self.pools = {k: torch.empty((blocks * self.page, width), dtype=model.dtype, device=self.device)
                       for k, width in model.cache_layers().items()}
         self.states = {k: (torch.zeros((max_seqs, max(taps - 1, 1), ch), dtype=torch.float32, device=self.device),
-                           torch.zeros((max_seqs, ch), dtype=torch.float32, device=self.device) if recurrent else None)
-                       for k, (taps, ch, recurrent) in model.state_layers().items()}
+                           torch.zeros((max_seqs, rec), dtype=torch.float32, device=self.device) if rec else None)
+                       for k, (taps, ch, rec) in model.state_layers().items()}
         self.live = {}
         self._next_idx = 0
 

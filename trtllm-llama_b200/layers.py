@@ -99,7 +99,7 @@ class GatedLinearRecurrence:
         return {}
 
     def conv_state(self):
-        return (self.taps, self.channels, True)
+        return (self.taps, self.channels, self.channels)
 
     def forward(self, x, ctx, rep=0):
         n, f32 = x.shape[0], torch.float32
@@ -151,7 +151,7 @@ class WindowedAttention:
         return {"own": self.kv_heads * (self.dim + self.vdim)}
 
     def conv_state(self):
-        return (self.taps, self.channels, False)
+        return (self.taps, self.channels, 0)
 
     def forward(self, x, ctx, rep=0):
         n, key = x.shape[0], (self.index, rep)
@@ -162,6 +162,109 @@ class WindowedAttention:
         o = ops.window_attention(q, ctx.pools[key], ctx.batch, ctx.page, self.kv_heads, self.vdim, self.scale, self.window,
                                  sink=self.sink, gate=proj[:, self.channels:] if self.gated else None)
         return ops.linear(o.view(n, self.heads * self.vdim), self.w_o, out_dtype=torch.float32)
+
+
+class DifferentialAttention:
+    """Grouped-query attention in which every query head holds TWO attention maps over one set of values; the head's output
+    is the first map's minus lambda times the second's, normalised.
+
+    q = W_q h has ``heads`` x 2 vectors of ``dim`` ([head][map]), k = W_k h has ``kv_heads`` x 2, v = W_v h has ``kv_heads``
+    vectors of ``vdim``; query head i reads key/value head i // (heads / kv_heads).  Every query and key vector is
+    RMS-normalised over dim with one weight for all queries and one for all keys; a query at position p is also multiplied by
+    the temperature 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) (temp_every 0: none).  Nothing is rotated.
+    a_m(i) = softmax_j(scale * q_m(i) . k_m(j)) v(j) over j <= i (and i - j < window, if one is given), m = 1, 2;
+    lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff;  o = a_1 - lambda a_2;  o <- o / sqrt(mean(o^2) + eps) * (1 - diff);
+    out = W_o concat_heads(o).
+
+    The three input projections are ONE product against the stacked rows, with the query rows reordered at load to
+    [kv head][map][head of the group]: the 2 * heads (head, map) queries are then plain grouped queries over 2 * kv_heads key
+    heads ([kv head][map], the stored order) whose neighbouring pairs share a value head, and the attention kernels of the
+    other models run them (``ops.window_attention`` with ``v_share`` = 2), returning both maps in fp32.  Per sequence the layer
+    keeps its normalised keys and its values in pages of a pool (entry = [2 kv_heads * dim keys | kv_heads * vdim values])."""
+
+    def __init__(self, index, *, heads, kv_heads, dim, vdim, scale, diff, eps, w_q, w_k, w_v, q_norm, k_norm, lq1, lk1, lq2, lk2,
+                 w_o, temp_coef=0.0, temp_every=0, window=0):
+        if heads % kv_heads:
+            raise ValueError(f"layer {index}: {heads} query heads do not split over {kv_heads} key/value heads")
+        per, width = heads // kv_heads, w_q.shape[1]
+        if w_q.shape[0] != heads * 2 * dim or w_k.shape[0] != kv_heads * 2 * dim or w_v.shape[0] != kv_heads * vdim:
+            raise ValueError(f"layer {index}: projections {tuple(w_q.shape)}, {tuple(w_k.shape)}, {tuple(w_v.shape)} do not hold two "
+                             f"maps of {heads} / {kv_heads} heads of {dim} and values of {vdim}")
+        self.index, self.heads, self.kv_heads, self.dim, self.vdim = index, heads, kv_heads, dim, vdim
+        self.scale, self.diff, self.eps, self.window = float(scale), float(diff), float(eps), int(window or 0)
+        self.temp_coef, self.temp_every = float(temp_coef), int(temp_every or 0)
+        self.dtype = w_q.dtype
+        w_q = w_q.view(kv_heads, per, 2, dim, width).permute(0, 2, 1, 3, 4).reshape(heads * 2 * dim, width)
+        self.w_in = torch.cat([w_q, w_k, w_v], dim=0).contiguous()
+        self.q_norm, self.k_norm, self.lam = q_norm, k_norm, (lq1, lk1, lq2, lk2)
+        self.w_o = w_o
+
+    def cache_entries(self):
+        return {"own": self.kv_heads * (2 * self.dim + self.vdim)}
+
+    def conv_state(self):
+        return None
+
+    def forward(self, x, ctx, rep=0):
+        n, pool = x.shape[0], ctx.pools[(self.index, rep)]
+        proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
+        q = ops.qk_norm_append(proj, self.q_norm, self.k_norm, self.eps, pool, ctx.batch, ctx.page, 2 * self.heads, 2 * self.kv_heads,
+                               self.dim, self.kv_heads * self.vdim, self.temp_coef, self.temp_every)
+        maps = ops.window_attention(q, pool, ctx.batch, ctx.page, 2 * self.kv_heads, self.vdim, self.scale, self.window, v_share=2,
+                                    out_f32=True)
+        o = ops.diff_combine(maps, *self.lam, self.diff, self.eps, 1.0 - self.diff, self.kv_heads, self.dtype)
+        return ops.linear(o.view(n, self.heads * self.vdim), self.w_o, out_dtype=torch.float32)
+
+
+class GatedDeltaRule:
+    """Recurrent layer with a matrix state per head that is updated by the delta rule under a learned decay (Yang, Kautz,
+    Hatamizadeh, "Gated Delta Networks: Improving Mamba2 with Delta Rule", 2024).
+
+    q = W_q h, k = W_k h (``kv_heads`` vectors of ``dim``), v = W_v h (``heads`` vectors of ``vdim``; head i reads query / key
+    head i // (heads / kv_heads)); every channel of q, k, v runs a causal convolution over ``taps`` inputs (the last tap weighs
+    the current one) and SiLU; q and k become unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q also times dim^-1/2.
+    beta = sigmoid(W_b h), g = exp(-exp(A_log) * softplus(W_a h + dt_bias)) per head.  Per head and token, in this order:
+        S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+    then o / sqrt(mean(o^2) + eps) * norm * silu(W_g h) per head, and W_o on the concatenated heads.
+
+    The six input projections are ONE product against the stacked [q | k | v | g | b | a] rows (fp32 out: beta, the decay
+    and everything else that enters the recurrence is fp32).  Per sequence the layer carries S (fp32, [heads, vdim, dim]) and
+    the last taps - 1 projected q | k | v rows in a state slot."""
+
+    def __init__(self, index, *, heads, kv_heads, dim, vdim, taps, eps, w_q, w_k, w_v, conv_q, conv_k, conv_v, w_b, w_a, a_log,
+                 dt_bias, norm, w_g, w_o, unit_eps=1e-6):
+        if heads % kv_heads:
+            raise ValueError(f"layer {index}: {heads} heads do not split over {kv_heads} query/key heads")
+        self.index, self.heads, self.kv_heads, self.dim, self.vdim, self.taps = index, heads, kv_heads, dim, vdim, int(taps)
+        self.eps, self.unit_eps, self.dtype = float(eps), float(unit_eps), w_q.dtype
+        self.channels = 2 * kv_heads * dim + heads * vdim
+        if w_q.shape[0] != kv_heads * dim or w_k.shape[0] != kv_heads * dim or w_v.shape[0] != heads * vdim \
+                or w_g.shape[0] != heads * vdim or w_b.shape[0] != heads or w_a.shape[0] != heads:
+            raise ValueError(f"layer {index}: projection shapes do not match {heads} heads of {vdim} over {kv_heads} x {dim}")
+        self.w_in = torch.cat([w_q, w_k, w_v, w_g, w_b, w_a], dim=0).contiguous()
+        self.col_g = self.channels
+        self.col_b = self.col_g + heads * vdim
+        self.col_a = self.col_b + heads
+        self.conv_w = torch.cat([conv_q, conv_k, conv_v], dim=0).contiguous()
+        if self.conv_w.shape != (self.channels, self.taps):
+            raise ValueError(f"layer {index}: convolution weights {tuple(self.conv_w.shape)} != {(self.channels, self.taps)}")
+        self.a_log, self.dt_bias, self.norm, self.w_o = a_log, dt_bias, norm, w_o
+
+    def cache_entries(self):
+        return {}
+
+    def conv_state(self):
+        return (self.taps, self.channels, self.heads * self.vdim * self.dim)
+
+    def forward(self, x, ctx, rep=0):
+        n = x.shape[0]
+        proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
+        conv_state, rec_state = ctx.states[(self.index, rep)]
+        u, bg = ops.delta_prepare(proj, self.conv_w, self.a_log, self.dt_bias, self.col_b, self.col_a, conv_state, ctx.batch,
+                                  self.heads, self.kv_heads, self.dim, self.vdim, self.unit_eps)
+        o = ops.delta_rule_scan(u, bg, rec_state, ctx.batch, self.heads, self.kv_heads, self.dim, self.vdim)
+        y = ops.gated_rmsnorm_heads(o, self.norm, self.eps, self.dtype, gate=proj[:, self.col_g:self.col_b])
+        return ops.linear(y.view(n, self.heads * self.vdim), self.w_o, out_dtype=torch.float32)
 
 
 class SquaredReluMLP:
@@ -176,47 +279,80 @@ class SquaredReluMLP:
 
 
 class RoutedExpertsMLP:
-    """Mixture of gated experts: each token runs ``top`` of ``experts`` small feed-forwards W_down (silu(W_gate h) * W_up h).
+    """Mixture of experts: each token runs ``top`` of ``experts`` small feed-forwards, gated ones
+    W_down (silu(W_gate h) * W_up h) or, without ``w_gate``, plain ones W_down act(W_up h) (``act``: squared ReLU, ...).
 
-    Router (fp32): s = sigmoid(W_router h); choice = s + correction; the experts form ``groups`` equal groups of
-    neighbours, a group scores the sum of its two largest choices and only the ``keep`` best groups stay eligible; the
-    ``top`` largest eligible choices are taken and weighted by their plain s (not renormalised).  The (token, choice)
-    pairs are sorted by expert on the device into whole tiles and both expert products walk that plan (tcgen05 tiles of
-    128 rows for bf16, warp-MMA / FMA tiles of 64 otherwise), so a step costs ``top`` experts per token whatever the
-    batch; a generation step's few pairs run one streaming product each instead."""
+    Router (fp32 logits W_router h), one of
+      ``"sigmoid_groups"``: s = sigmoid(logit); choice = s + correction; the experts form ``groups`` equal groups of
+        neighbours, a group scores the sum of its two largest choices and only the ``keep`` best groups stay eligible; the
+        ``top`` largest eligible choices are taken and weighted by their plain s (not renormalised);
+      ``"softmax"``: s = softmax over all experts; the ``top`` largest are taken and weighted by s / (sum of the chosen s +
+        1e-20) * ``route_scale`` (``renorm``) or s * ``route_scale``.
+    ``shared``: a feed-forward every token runs besides (anything with ``forward(x, ctx)``); its output joins the weighted sum.
+    The (token, choice) pairs are sorted by expert on the device into whole tiles and both expert products walk that plan
+    (tcgen05 tiles of 128 rows for bf16, warp-MMA / FMA tiles of 64 otherwise), so a step costs ``top`` experts per token
+    whatever the batch; a generation step's few pairs run one streaming product each instead."""
 
-    def __init__(self, *, w_router, correction, w_gate, w_up, w_down, top, groups=1, keep=1):
+    def __init__(self, *, w_router, w_up, w_down, top, w_gate=None, correction=None, groups=1, keep=1, router="sigmoid_groups",
+                 renorm=True, route_scale=1.0, act=ops.ACT_RELU_SQUARED, shared=None):
         """w_gate, w_up: [experts, ff, width]; w_down: [experts, width, ff]."""
-        self.experts, self.top, self.groups, self.keep = w_gate.shape[0], int(top), int(groups), int(keep)
+        self.experts, self.top, self.groups, self.keep = w_up.shape[0], int(top), int(groups), int(keep)
         if self.experts % self.groups or not 1 <= self.keep <= self.groups or not 1 <= self.top <= self.experts:
             raise ValueError(f"router: {self.experts} experts, {groups} groups (keep {keep}), top {top}")
+        if router not in ("sigmoid_groups", "softmax"):
+            raise ValueError(f"unknown router kind {router!r}")
+        self.router, self.renorm, self.route_scale, self.shared = router, bool(renorm), float(route_scale), shared
         self.w_router, self.correction = w_router, correction
-        self.w_gate_up = torch.cat([w_gate, w_up], dim=1).contiguous()      # [experts, 2 ff, width]: gate rows, then up rows
+        self.gated, self.act = w_gate is not None, int(act)
+        if self.gated:
+            self.w_gate_up = torch.cat([w_gate, w_up], dim=1).contiguous()      # [experts, 2 ff, width]: gate rows, then up rows
+        else:
+            self.w_up = w_up.contiguous()
         self.w_down, self.dtype = w_down.contiguous(), w_down.dtype
 
     def forward(self, x, ctx):
         n, top, K = x.shape[0], self.top, x.shape[1]
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32, compute=ops.COMPUTE_FMA32)
-        ids, weights = ops.moe_route(logits, self.correction, top, self.groups, self.keep)
+        if self.router == "softmax":
+            ids, weights = ops.moe_route_softmax(logits, top, self.renorm, self.route_scale)
+        else:
+            ids, weights = ops.moe_route(logits, self.correction, top, self.groups, self.keep)
+        add = self.shared.forward(x, ctx) if self.shared is not None else None
         bf16 = self.dtype == torch.bfloat16
+        if not self.gated:
+            # plain experts: the activation is the up projection's epilogue in every kernel
+            if bf16 and n * top <= ops.MOE_GEMV_MAX_PAIRS and not ops.FORCE_TILE_LINEAR:
+                h = ops.moe_gemv(x, self.w_up, ids, a_div=top, out_dtype=self.dtype, act=self.act)
+                y = ops.moe_gemv(h, self.w_down, ids, a_div=0, out_dtype=torch.float32) if h is not None else None
+                if y is not None:
+                    return ops.moe_combine(y, weights, add=add)
+            if bf16 and n * top >= ops.TC_MIN_ROWS and K % 8 == 0 and self.w_down.shape[2] % 8 == 0 and not ops.FORCE_TILE_LINEAR:
+                slot_pair, tile_expert, pair_slot = ops.moe_plan(ids, self.experts, ops.MOE_TILE_TC)
+                h = ops.moe_linear_tc(ops.moe_gather_rows(x, slot_pair, top), self.w_up, tile_expert, self.dtype, act=self.act)
+                y = ops.moe_linear_tc(h, self.w_down, tile_expert, torch.float32)
+                return ops.moe_combine(y, weights, pair_slot, add=add)
+            slot_pair, tile_expert, pair_slot = ops.moe_plan(ids, self.experts, ops.MOE_TILE)
+            h = ops.moe_linear(x, self.w_up, slot_pair, tile_expert, a_div=top, out_dtype=self.dtype, act=self.act)
+            y = ops.moe_linear(h, self.w_down, slot_pair, tile_expert, a_div=0, out_dtype=torch.float32)
+            return ops.moe_combine(y, weights, pair_slot, add=add)
         if bf16 and n * top <= ops.MOE_GEMV_MAX_PAIRS and not ops.FORCE_TILE_LINEAR:
             # generation steps: one streaming product per pair, gate / up and the activation in one kernel, no plan
             act = ops.moe_gemv(x, self.w_gate_up, ids, a_div=top, out_dtype=self.dtype, gated=True)
             y = ops.moe_gemv(act, self.w_down, ids, a_div=0, out_dtype=torch.float32) if act is not None else None
             if y is not None:
-                return ops.moe_combine(y, weights)
+                return ops.moe_combine(y, weights, add=add)
         if bf16 and n * top >= ops.TC_MIN_ROWS and K % 8 == 0 and self.w_down.shape[2] % 8 == 0 and not ops.FORCE_TILE_LINEAR:
             # prompt-sized steps: the tcgen05 kernel over a plan of 128-row tiles
             slot_pair, tile_expert, pair_slot = ops.moe_plan(ids, self.experts, ops.MOE_TILE_TC)
             gu = ops.moe_linear_tc(ops.moe_gather_rows(x, slot_pair, top), self.w_gate_up, tile_expert, torch.float32)
             act = ops.gated_act(gu, self.dtype, 1.0, 0.0, 0.0)              # silu(gate) * up
             y = ops.moe_linear_tc(act, self.w_down, tile_expert, torch.float32)
-            return ops.moe_combine(y, weights, pair_slot)
+            return ops.moe_combine(y, weights, pair_slot, add=add)
         slot_pair, tile_expert, pair_slot = ops.moe_plan(ids, self.experts, ops.MOE_TILE)
         gu = ops.moe_linear(x, self.w_gate_up, slot_pair, tile_expert, a_div=top, out_dtype=torch.float32)
         act = ops.gated_act(gu, self.dtype, 1.0, 0.0, 0.0)
         y = ops.moe_linear(act, self.w_down, slot_pair, tile_expert, a_div=0, out_dtype=torch.float32)
-        return ops.moe_combine(y, weights, pair_slot)
+        return ops.moe_combine(y, weights, pair_slot, add=add)
 
 
 class ClampedGatedMLP:
@@ -244,15 +380,28 @@ class LayerStackModel:
     x <- x + residual_mult * norm_post(f(norm_pre(x))).  Norm weights are stored around ``norm_offset`` below 1 (the
     multiplier is w + norm_offset).
 
+    ``parallel``: the layer's sublayers run side by side on ONE normalised input instead, x <- x + residual_mult *
+    (mixer(h) + mlp(h)) with h = norm(x; ``pre1``).  ``norm`` = "layer" (parallel layers and the output norm): layer norm
+    (x - mean) / sqrt(var + eps) * w + b with the biases in ``pre1_b`` / ``final_norm_b``; "rms": the RMS norm above.
+
     ``loop`` = (start, stop, times): layers start .. stop - 1 run ``times`` times in a row with the same weights; every
-    pass has caches and states of its own, and row t of ``loop_step`` is added to the residual stream right before pass
-    t's first layer.  ``logit_cap`` > 0: logits <- cap * tanh(logits / cap)."""
+    pass has caches and states of its own.  Right before pass t's first layer row t of ``loop_step`` is added to the residual
+    stream, and / or the stream is re-projected together with the embedding output x0, x <- ``loop_in`` [x ; x0] (``loop_in``
+    [width, 2 width], the stream's columns first).  ``logit_cap`` > 0: logits <- cap * tanh(logits / cap)."""
 
     def __init__(self, *, vocab, width, dtype, embed, layers, final_norm, head, eps, embed_scale=1.0, norm_offset=0.0,
-                 residual_mult=1.0, loop=None, loop_step=None, logit_cap=0.0):
+                 residual_mult=1.0, loop=None, loop_step=None, logit_cap=0.0, norm="rms", parallel=False, final_norm_b=None,
+                 loop_in=None):
         self.vocab, self.width, self.dtype, self.eps, self.norm_offset = vocab, width, dtype, float(eps), float(norm_offset)
         self.embed, self.embed_scale, self.layers, self.final_norm, self.head = embed, float(embed_scale), layers, final_norm, head
         self.residual_mult, self.logit_cap, self.loop_step = float(residual_mult), float(logit_cap or 0.0), loop_step
+        if norm not in ("rms", "layer"):
+            raise ValueError(f"unknown norm kind {norm!r}")
+        if (norm == "layer") != bool(parallel):
+            raise NotImplementedError("layer norm goes with side-by-side sublayers, RMS norm with sublayers in a row")
+        self.norm, self.parallel, self.final_norm_b, self.loop_in = norm, bool(parallel), final_norm_b, loop_in
+        if loop_in is not None and tuple(loop_in.shape) != (width, 2 * width):
+            raise ValueError(f"loop input projection {tuple(loop_in.shape)} != {(width, 2 * width)}")
         for l in layers:
             for k in ("pre1", "post1", "pre2", "post2"):
                 l.setdefault(k, None)
@@ -285,6 +434,10 @@ class LayerStackModel:
         Each sublayer is x <- x + residual_mult * norm_post(f(norm_pre(x))).  Where the next sublayer has a norm on its
         input and nothing is added to x in between, its input comes out of the same kernel as this sublayer's residual
         update (``ops.residual_norm_rows``)."""
+        if self.parallel:
+            return self._forward_parallel(ctx, on_layer)
+        if self.loop_in is not None:
+            raise NotImplementedError("loop input projection with sublayers in a row")
         x = ops.embed_scaled(self.embed, ctx.batch.tok_ids, self.embed_scale)
         subs = []                                   # (function of h, pre weight, post weight, step vector, run if it ends one)
         for run, (i, t, first) in enumerate(self.runs):
@@ -312,7 +465,40 @@ class LayerStackModel:
                 on_layer(ends_run, x)
         return x
 
+    def _forward_parallel(self, ctx, on_layer=None):
+        """Layers whose mixer and feed-forward read one layer-normalised input.  The residual step of a layer and the next
+        layer's norm are ONE kernel (``ops.residual_layernorm_rows``) unless the stream is re-projected in between."""
+        x = ops.embed_scaled(self.embed, ctx.batch.tok_ids, self.embed_scale)
+        reproject = self.loop_in is not None
+        x0 = x.clone() if reproject and not self.runs[0][2] else x      # layers ahead of the looped block update x in place
+        h = None
+        for run, (i, t, first) in enumerate(self.runs):
+            l = self.layers[i]
+            if first and self.loop_step is not None:
+                ops.add_row_vector(x, self.loop_step[t])
+                h = None
+            if first and reproject:
+                x, h = ops.linear(ops.concat_rows(x, x0, self.dtype), self.loop_in, out_dtype=torch.float32), None
+            if h is None:
+                h = ops.layernorm_rows(x, l["pre1"], l.get("pre1_b"), self.eps, out_dtype=self.dtype)
+            y1 = l["mixer"].forward(h, ctx, t)
+            y2 = l["mlp"].forward(h, ctx) if l["mlp"] is not None else None
+            nxt = self.runs[run + 1] if run + 1 < len(self.runs) else None
+            if nxt is not None and not (nxt[2] and (reproject or self.loop_step is not None)):
+                nl = self.layers[nxt[0]]
+                h = ops.residual_layernorm_rows(x, y1, y2, self.residual_mult, nl["pre1"], nl.get("pre1_b"), self.eps, self.dtype)
+            else:
+                ops.residual_layernorm_rows(x, y1, y2, self.residual_mult)
+                h = None
+            if on_layer is not None:
+                on_layer(run, x)
+        return x
+
     def logits(self, x, rows_idx):
+        if self.norm == "layer":
+            h = ops.layernorm_rows(x, self.final_norm, self.final_norm_b, self.eps, out_dtype=self.dtype, rows_idx=rows_idx)
+            z = ops.linear(h, self.head, out_dtype=torch.float32)
+            return ops.tanh_cap(z, self.logit_cap) if self.logit_cap > 0 else z
         h = ops.rmsnorm_rows(x, self.final_norm, self.eps, self.norm_offset, out_dtype=self.dtype, rows_idx=rows_idx)
         z = ops.linear(h, self.head, out_dtype=torch.float32)
         return ops.tanh_cap(z, self.logit_cap) if self.logit_cap > 0 else z

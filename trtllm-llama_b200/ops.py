@@ -592,13 +592,15 @@ def qkv_conv_rope_append(proj, conv_w, state, table, dims, pool, batch, page, he
     return q
 
 
-def window_attention(q, pool, batch, page, kv_heads, vdim, scale, window, sink=None, gate=None):
+def window_attention(q, pool, batch, page, kv_heads, vdim, scale, window, sink=None, gate=None, v_share=1, out_f32=False):
     """Grouped-query attention of every row over the last ``window`` cached positions of its sequence (0: all), with an
-    optional softmax sink per head and an optional per-head sigmoid gate (fp32 logits [N, >= heads], any row stride)."""
+    optional softmax sink per head and an optional per-head sigmoid gate (fp32 logits [N, >= heads], any row stride).
+    ``v_share`` > 1: neighbouring key heads share a value head (key head g reads value head g // v_share; the pool entry
+    holds kv_heads key heads and kv_heads // v_share value heads).  ``out_f32``: the result is fp32 in every storage mode."""
     _chk_cuda(q, pool, sink)
     _chk_dev(gate)
     rows, heads, dim = q.shape
-    out = torch.empty((rows, heads, vdim), dtype=q.dtype, device=q.device)
+    out = torch.empty((rows, heads, vdim), dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
     if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1):
         raise ValueError("gate logits are fp32 with unit inner stride")
     nsplit, ws = 1, None
@@ -609,12 +611,126 @@ def window_attention(q, pool, batch, page, kv_heads, vdim, scale, window, sink=N
         nsplit = max(1, min(32, 296 // ctas, span // 64 + 1))
         if nsplit > 1:
             ws = torch.empty((rows * heads * nsplit * (vdim + 2),), dtype=torch.float32, device=q.device)
-    check(_rl.tb_window_attention(_p(out), _p(q), _p(pool), _dt(pool), _p(gate), gate.stride(0) if gate is not None else 0,
-                                  _p(sink), _dt(sink) if sink is not None else 0, _p(batch.tok_seq), _p(batch.tok_pos),
-                                  _p(batch.block_table), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
-                                  batch.num_seqs, batch.max_len, batch.max_blocks, page, rows, heads, kv_heads, dim, vdim,
-                                  float(scale), int(window), 1 if FORCE_SIMT_ATTENTION else 0, nsplit, _p(ws), _stream()),
-          "tb_window_attention")
+    check(_rl.tb_window_attention_shared_values(
+        _p(out), int(out_f32), _p(q), _p(pool), _dt(pool), _p(gate), gate.stride(0) if gate is not None else 0, _p(sink),
+        _dt(sink) if sink is not None else 0, _p(batch.tok_seq), _p(batch.tok_pos), _p(batch.block_table), _p(batch.seq_start),
+        _p(batch.seq_len), _p(batch.seq_past), batch.num_seqs, batch.max_len, batch.max_blocks, page, rows, heads, kv_heads,
+        int(v_share), dim, vdim, float(scale), int(window), 1 if FORCE_SIMT_ATTENTION else 0, nsplit, _p(ws), _stream()),
+        "tb_window_attention_shared_values")
+    return out
+
+
+def qk_norm_append(proj, w_q, w_k, eps, pool, batch, page, q_vectors, k_vectors, dim, v_channels, temp_coef=0.0, temp_every=0):
+    """Projected rows (fp32 [N, >= (q_vectors + k_vectors) * dim + v_channels]) -> RMS norm of every query and key vector
+    over ``dim`` (weights [dim] or None), the queries' position temperature 1 + coef * ln(floor((pos + 1) / every) + 1)
+    (every 0: none) -> queries [N, q_vectors, dim] in the pool's type, keys and values into the pages."""
+    _chk_dev(proj, w_q, w_k, pool)
+    rows = proj.shape[0]
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[1] < (q_vectors + k_vectors) * dim + v_channels:
+        raise ValueError("qk_norm_append: proj fp32 [N, >= (q_vectors + k_vectors) * dim + v_channels]")
+    if pool.shape[1] != k_vectors * dim + v_channels:
+        raise ValueError("qk_norm_append: pool entry != k_vectors * dim + v_channels")
+    w = w_q if w_q is not None else w_k
+    q = torch.empty((rows, q_vectors, dim), dtype=pool.dtype, device=proj.device)
+    check(_rl.tb_qk_norm_append(_p(q), _p(pool), _dt(pool), _p(proj), proj.stride(0), _p(w_q), _p(w_k), _dt(w) if w is not None else 0,
+                                float(eps), float(temp_coef), int(temp_every), _p(batch.tok_seq), _p(batch.tok_pos),
+                                _p(batch.block_table), batch.max_blocks, page, rows, q_vectors, k_vectors, dim, v_channels, _stream()),
+          "tb_qk_norm_append")
+    return q
+
+
+def diff_combine(maps, lq1, lk1, lq2, lk2, diff, eps, mult, kv_heads, out_dtype):
+    """maps fp32 [N, kv_heads * 2 * per, vdim] (per key/value head: map 1 of its ``per`` heads, then map 2) -> [N, kv_heads *
+    per, vdim] = rms_normalised(map1 - lambda map2) * mult, lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff."""
+    _chk_cuda(maps, lq1, lk1, lq2, lk2)
+    rows, h2, vdim = maps.shape
+    per = h2 // (2 * kv_heads)
+    if maps.dtype != torch.float32 or per * 2 * kv_heads != h2:
+        raise ValueError("diff_combine: maps fp32 [N, kv_heads * 2 * per, vdim]")
+    out = torch.empty((rows, kv_heads * per, vdim), dtype=out_dtype, device=maps.device)
+    check(_rl.tb_diff_combine(_p(out), _dt(out), _p(maps), _p(lq1), _p(lk1), _p(lq2), _p(lk2), _dt(lq1), lq1.numel(), float(diff),
+                              float(eps), float(mult), rows, kv_heads, per, vdim, _stream()), "tb_diff_combine")
+    return out
+
+
+def delta_prepare(proj, conv_w, a_log, dt_bias, col_b, col_a, conv_state, batch, heads, kv_heads, dim, vdim, eps_unit=1e-6):
+    """Stacked projection rows (fp32; q | k | v first) -> (u fp32 [N, C]: unit q / sqrt(dim) | unit k | v after convolution
+    and SiLU, bg fp32 [N, 2 heads]: beta | decay); then the carried convolution inputs move on."""
+    _chk_dev(proj, conv_w, a_log, dt_bias, conv_state)
+    rows, taps = proj.shape[0], conv_w.shape[1]
+    C = 2 * kv_heads * dim + heads * vdim
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or conv_w.shape[0] != C or not conv_w.is_contiguous():
+        raise ValueError("delta_prepare: proj fp32 rows, conv_w [C, taps] contiguous")
+    u = torch.empty((rows, C), dtype=torch.float32, device=proj.device)
+    bg = torch.empty((rows, 2 * heads), dtype=torch.float32, device=proj.device)
+    st = _p(conv_state) if taps > 1 else None
+    check(_rl.tb_delta_prepare(_p(u), _p(bg), _p(proj), proj.stride(0), _p(conv_w), _p(a_log), _p(dt_bias), _dt(conv_w), int(col_b),
+                               int(col_a), st, st, _p(batch.tok_seq), _p(batch.tok_pos), _p(batch.seq_start), _p(batch.seq_len),
+                               _p(batch.seq_past), _p(batch.seq_slot), rows, heads, kv_heads, dim, vdim, taps, float(eps_unit),
+                               _stream()), "tb_delta_prepare")
+    if taps > 1 and batch.max_len > 1:       # sequences that bring one row were moved on by the kernel above
+        check(_rl.tb_causal_conv1d_update(_p(conv_state), _p(proj), proj.stride(0), _p(batch.seq_start), _p(batch.seq_len),
+                                          _p(batch.seq_past), _p(batch.seq_slot), batch.num_seqs, C, taps, 1, _stream()),
+              "tb_causal_conv1d_update")
+    return u, bg
+
+
+def delta_rule_scan(u, bg, state, batch, heads, kv_heads, dim, vdim):
+    """The gated delta rule over every sequence's rows, from and into ``state`` (fp32 [slots, heads * vdim * dim])."""
+    _chk_cuda(u, bg, state)
+    out = torch.empty((u.shape[0], heads, vdim), dtype=torch.float32, device=u.device)
+    check(_rl.tb_delta_rule_scan(_p(out), _p(u), _p(bg), _p(state), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
+                                 _p(batch.seq_slot), batch.num_seqs, heads, kv_heads, dim, vdim, _stream()), "tb_delta_rule_scan")
+    return out
+
+
+def gated_rmsnorm_heads(o, w, eps, out_dtype, gate=None):
+    """o fp32 [N, heads, vdim] -> o / rms(o) * w * silu(gate) per head (gate: fp32 logits [N, >= heads * vdim], any row stride)."""
+    _chk_dev(o, w, gate)
+    rows, heads, vdim = o.shape
+    if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1):
+        raise ValueError("gate logits are fp32 with unit inner stride")
+    out = torch.empty((rows, heads, vdim), dtype=out_dtype, device=o.device)
+    check(_rl.tb_gated_rmsnorm_heads(_p(out), _dt(out), _p(o), _p(gate), gate.stride(0) if gate is not None else 0, _p(w),
+                                     _dt(w) if w is not None else 0, float(eps), rows, heads, vdim, _stream()), "tb_gated_rmsnorm_heads")
+    return out
+
+
+def layernorm_rows(x, w, b, eps, out_dtype=torch.float32, rows_idx=None):
+    """Layer norm with weight and bias of fp32 rows (row r of the result from row rows_idx[r] when given)."""
+    _chk_dev(x, w, b, rows_idx)
+    if x.dtype != torch.float32 or x.stride(1) != 1:
+        raise ValueError("layernorm_rows normalises fp32 rows")
+    rows = x.shape[0] if rows_idx is None else rows_idx.numel()
+    out = torch.empty((rows, x.shape[1]), dtype=out_dtype, device=x.device)
+    check(_rl.tb_layernorm_rows(_p(out), _dt(out), out.stride(0), _p(x), x.stride(0), _p(w), _p(b), _dt(w), float(eps), _p(rows_idx),
+                                rows, x.shape[1], _stream()), "tb_layernorm_rows")
+    return out
+
+
+def residual_layernorm_rows(x, y1, y2, out_scale, w=None, b=None, eps=0.0, out_dtype=torch.float32):
+    """x += out_scale * (y1 + y2) in place (y2 may be None); with ``w`` also returns layer_norm(x; w, b) — the residual step of
+    a layer with side-by-side sublayers and the next layer's input in one kernel."""
+    _chk_dev(x, y1, y2, w, b)
+    for t in (x, y1, y2):
+        if t is not None and (t.dtype != torch.float32 or t.stride(1) != 1):
+            raise ValueError("residual_layernorm_rows: fp32 rows")
+    h = torch.empty(x.shape, dtype=out_dtype, device=x.device) if w is not None else None
+    check(_rl.tb_residual_layernorm_rows(_p(x), x.stride(0), _p(y1), y1.stride(0), _p(y2), y2.stride(0) if y2 is not None else 0,
+                                         float(out_scale), _p(w), _p(b), _dt(w) if w is not None else 0, float(eps), _p(h),
+                                         _dt(h) if h is not None else 0, h.stride(0) if h is not None else 0, x.shape[0], x.shape[1],
+                                         _stream()), "tb_residual_layernorm_rows")
+    return h
+
+
+def concat_rows(a, b, out_dtype):
+    """[a | b] row by row (fp32 inputs) as one contiguous operand of type ``out_dtype``."""
+    _chk_dev(a, b)
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.stride(1) != 1 or b.stride(1) != 1 or a.shape[0] != b.shape[0]:
+        raise ValueError("concat_rows: two fp32 row sets of equal height")
+    out = torch.empty((a.shape[0], a.shape[1] + b.shape[1]), dtype=out_dtype, device=a.device)
+    check(_rl.tb_concat_rows(_p(out), _dt(out), _p(a), a.stride(0), a.shape[1], _p(b), b.stride(0), b.shape[1], a.shape[0], _stream()),
+          "tb_concat_rows")
     return out
 
 
@@ -632,6 +748,18 @@ def moe_route(logits, correction, top, groups, keep):
     check(_rl.tb_moe_route(_p(ids), _p(weights), _p(logits.contiguous()), _p(correction),
                            _dt(correction) if correction is not None else 0, rows, experts, top, groups, keep, _stream()),
           "tb_moe_route")
+    return ids, weights
+
+
+def moe_route_softmax(logits, top, renorm=True, scale=1.0):
+    """-> (ids int32 [N, top], weights fp32 [N, top]): softmax over all experts, the ``top`` largest, weights = score / (sum of
+    the chosen + 1e-20) * scale (renorm) or score * scale."""
+    _chk_cuda(logits)
+    rows, experts = logits.shape
+    ids = torch.empty((rows, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((rows, top), dtype=torch.float32, device=logits.device)
+    check(_rl.tb_moe_route_softmax(_p(ids), _p(weights), _p(logits.contiguous()), rows, experts, top, int(bool(renorm)), float(scale),
+                                   _stream()), "tb_moe_route_softmax")
     return ids, weights
 
 
@@ -684,29 +812,32 @@ def moe_linear_tc(xs, w, tile_expert, out_dtype, act=ACT_NONE):
     return out
 
 
-def moe_gemv(a, w, ids, *, a_div, out_dtype, gated=False):
+def moe_gemv(a, w, ids, *, a_div, out_dtype, gated=False, act=ACT_NONE):
     """Expert products for few pairs without a plan: pair b against expert ids[b].  gated: w [experts, 2 N, K] and the
-    result is silu(gate) * up.  Returns None when the streaming kernel does not take the shape."""
+    result is silu(gate) * up; else ``act`` is applied.  Returns None when the streaming kernel does not take the shape."""
     _chk_dev(a, w, ids)
     E, rows_w, K = w.shape
     N = rows_w // 2 if gated else rows_w
     pairs = ids.numel()
     out = torch.empty((pairs, N), dtype=out_dtype, device=a.device)
     rc = _rl.tb_moe_gemv(_p(out), _dt(out), out.stride(0), _p(a), _dt(a), a.stride(0), _p(w), _dt(w), _p(ids), pairs, int(a_div),
-                         N, K, 2 if gated else ACT_NONE, 1.0, 0.0, _stream())
+                         N, K, 2 if gated else act, 1.0, 0.0, _stream())
     if rc == -3:
         return None
     check(rc, "tb_moe_gemv")
     return out
 
 
-def moe_combine(y, weights, pair_slot=None):
-    """out[n] = sum_k weights[n, k] * y[row of pair n * top + k]  (fp32); the pair's row is pair_slot[pair], or the pair's
-    index when ``y`` is in pair order."""
-    _chk_cuda(y, weights, pair_slot)
+def moe_combine(y, weights, pair_slot=None, add=None):
+    """out[n] = add[n] + sum_k weights[n, k] * y[row of pair n * top + k]  (fp32); the pair's row is pair_slot[pair], or the
+    pair's index when ``y`` is in pair order.  ``add``: fp32 [N, width] every token has besides (a shared expert), or None."""
+    _chk_cuda(y, weights, pair_slot, add)
     rows, top = weights.shape
     out = torch.empty((rows, y.shape[1]), dtype=torch.float32, device=y.device)
-    check(_rl.tb_moe_combine(_p(out), _p(y), _p(weights), _p(pair_slot), rows, y.shape[1], top, _stream()), "tb_moe_combine")
+    if add is not None and (add.dtype != torch.float32 or add.shape != out.shape):
+        raise ValueError("moe_combine: add is fp32 [N, width]")
+    check(_rl.tb_moe_combine_add(_p(out), _p(y), _p(weights), _p(pair_slot), _p(add), rows, y.shape[1], top, _stream()),
+          "tb_moe_combine_add")
     return out
 
 
