@@ -193,9 +193,10 @@ def random_mimolix(layers, *, width=48, vocab=61, eps=1e-5, residual_mult=0.8, e
     tensors) in the checkpoint's naming; values are rounded to ``dtype`` so that product and oracle start from the same
     numbers.
 
-    ``spaced_router``: the router's rows are multiples of ONE direction with well separated factors and the layer norm's
-    bias has a component along it, so every token ranks the experts alike by a wide margin: a run in reduced precision can
-    then be compared position by position without a close call deciding which experts ran."""
+    ``spaced_router``: the router's rows are multiples (steps of 0.3) of ONE unit direction and the layer norm's bias has a
+    component of 6 along it, while the normalised stream's own component along a unit direction is of order 1: every token
+    ranks the experts alike with logits about 1.8 apart, so a run in reduced precision can be compared position by position
+    without a close call deciding which experts ran, and the chosen experts still share the weight."""
     g = torch.Generator().manual_seed(seed)
 
     def n(*shape, std=None, mean=0.0):
@@ -237,8 +238,8 @@ def random_mimolix(layers, *, width=48, vocab=61, eps=1e-5, residual_mult=0.8, e
                 direction = torch.randn(width, generator=g)
                 direction = direction / direction.norm()
                 factors = torch.randperm(E, generator=g).double() - (E - 1) / 2
-                t[p + "mlp.router"] = (factors[:, None] * direction[None, :] * 3.0).to(dtype)
-                t[p + "norm1.b"] = (t[p + "norm1.b"].double() + 4.0 * direction).to(dtype)
+                t[p + "mlp.router"] = (factors[:, None] * direction[None, :] * 0.3).to(dtype)
+                t[p + "norm1.b"] = (t[p + "norm1.b"].double() + 6.0 * direction).to(dtype)
             for e in range(E):
                 t.update({f"{p}mlp.e{e}.up": n(ff, width, std=2.0 * width ** -0.5), f"{p}mlp.e{e}.down": n(width, ff)})
             if shared:
