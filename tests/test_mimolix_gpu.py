@@ -280,6 +280,7 @@ def test_query_temperature_steps(dtype, every, coef):
     """The temperature steps where floor((p + 1) / every) does: positions every - 2, every - 1 (the first with one whole block)
     and the multiples after it, as a prompt and decoded one by one behind a prompt that ends right before a step."""
     page, H, G, d, dv = 16, 2, 1, 16, 8
+    sc = 0.9 if dtype == torch.float32 else 0.15        # bf16 queries and keys: scores small enough that their rounding stays small
     P = max(3 * every + 2, 8)
     g = torch.Generator().manual_seed(every)
     q, k, v = torch.randn(P, H, 2, d, generator=g), torch.randn(P, G, 2, d, generator=g), torch.randn(P, G, dv, generator=g)
@@ -293,8 +294,8 @@ def test_query_temperature_steps(dtype, every, coef):
         lam = O.differential_lambda(dict(zip(("lq1", "lk1", "lq2", "lk2"), [x.to(dtype).double() for x in lam4])), "", 0.4)
         out = torch.zeros(P, H, dv, dtype=torch.float64)
         for h in range(H):
-            a1 = O.causal_softmax_attention(qn[:, h, 0], kn[:, 0, 0], v[:, 0].double(), 0.9)
-            a2 = O.causal_softmax_attention(qn[:, h, 1], kn[:, 0, 1], v[:, 0].double(), 0.9)
+            a1 = O.causal_softmax_attention(qn[:, h, 0], kn[:, 0, 0], v[:, 0].double(), sc)
+            a2 = O.causal_softmax_attention(qn[:, h, 1], kn[:, 0, 1], v[:, 0].double(), sc)
             out[:, h] = O.rms(a1 - lam * a2, 1e-5) * 0.6
         return out
     want = plain(coef, every)
@@ -302,7 +303,7 @@ def test_query_temperature_steps(dtype, every, coef):
         assert (want[every - 1] - plain(0.0, 1)[every - 1]).abs().max() > 1e-3, "the temperature does not show at its first step"
     blocks = torch.randperm(-(-P // page), generator=g).tolist()
     for cuts in ([P], [max(every - 1, 1)] + [1] * (P - max(every - 1, 1))):
-        got = _diff_attention_ops(q, k, v, lam4, 0.9, 0.4, 1e-5, coef, every, cuts, dtype, page, blocks, wq.to(dtype).cuda(), wk.to(dtype).cuda())
+        got = _diff_attention_ops(q, k, v, lam4, sc, 0.4, 1e-5, coef, every, cuts, dtype, page, blocks, wq.to(dtype).cuda(), wk.to(dtype).cuda())
         _close(got, want, dtype, f"temperature every {every}, cuts {cuts[:3]}", scale=2.0)
 
 
@@ -331,7 +332,7 @@ def test_differential_attention_head_sizes(d, dv, H, G):
 
 
 @pytest.mark.parametrize("cuts", [[600], [1] * 40 + [560], [17, 16, 15, 2, 250, 300], [599, 1]])
-@pytest.mark.parametrize("H,G,d,dv", [(4, 2, 16, 12), (2, 1, 64, 8), (3, 3, 40, 33)])
+@pytest.mark.parametrize("H,G,d,dv", [(4, 2, 16, 12), (2, 1, 64, 8), (3, 3, 40, 33), (16, 4, 128, 80), (40, 8, 24, 32)])
 def test_delta_rule_remembers_far_tokens(H, G, d, dv, cuts):
     """The recurrence over 600 tokens with decays close to 1, so that what was written hundreds of tokens ago still decides the
     read-out: cut into portions (state carried in a slot that held another sequence's state) against the plain loop."""
@@ -347,14 +348,19 @@ def test_delta_rule_remembers_far_tokens(H, G, d, dv, cuts):
     assert (want[-1] - recent[-1]).abs().max() > 1e-2 * want[-1].abs().max(), "the first 300 tokens do not show at the end"
     u = torch.cat([q.reshape(P, -1), k.reshape(P, -1), v.reshape(P, -1)], dim=1).float().cuda()
     bg = torch.cat([beta, dec], dim=1).float().cuda()
-    state = torch.full((3, H * dv * d), 9.0, device="cuda")
-    at, outs = 0, []
-    for n in cuts:
-        b = RaggedBatch([([0] * n, at, 1, [0])], [], "cuda")
-        outs.append(ops.delta_rule_scan(u[at:at + n], bg[at:at + n], state, b, H, G, d, dv))
-        at += n
-    _close(torch.cat(outs), want, torch.float32, f"delta rule over {P} tokens, cuts {cuts[:4]}")
-    assert bool((state[0] == 9.0).all()) and bool((state[2] == 9.0).all()), "another slot's state was touched"
+    for serial in (False, True):              # eight rows at a time (portions of three rows and more), and row by row
+        ops.FORCE_SERIAL_SCAN = serial
+        try:
+            state = torch.full((3, H * dv * d), 9.0, device="cuda")
+            at, outs = 0, []
+            for n in cuts:
+                b = RaggedBatch([([0] * n, at, 1, [0])], [], "cuda")
+                outs.append(ops.delta_rule_scan(u[at:at + n], bg[at:at + n], state, b, H, G, d, dv))
+                at += n
+        finally:
+            ops.FORCE_SERIAL_SCAN = False
+        _close(torch.cat(outs), want, torch.float32, f"delta rule over {P} tokens, cuts {cuts[:4]}, row by row: {serial}")
+        assert bool((state[0] == 9.0).all()) and bool((state[2] == 9.0).all()), "another slot's state was touched"
 
 
 # ---------------------------------------------------------------------------------------------------------------

@@ -13,6 +13,19 @@
 //                          token chunk is staged) the step is u = beta (v - g a), o = g b + u (k . q), S <- g S + k u: one
 //                          reduction round per token instead of two dependent ones.  Tokens are staged through shared memory
 //                          in chunks of 16.  State layout per slot: [heads][vdim][dim] (a column's elements are contiguous).
+//                          For steps whose sequences bring a token or two (generation).
+//   delta_scan_blocked_kernel   prompt portions: the same recurrence resolved EIGHT tokens at a time.  With S the state ahead of the
+//                          block, D_j the product of the block's decays up to token j, and the block's own products
+//                          KK_ij = k_i . k_j, KQ_ij = k_i . q_j (i <= j; delta_gram_kernel computes them once per query / key head):
+//                              a_j = D_j (S^T k_j) + sum_{i<j} (D_j / D_i) KK_ij u_i,    u_j = beta_j (v_j - a_j),
+//                              o_j = D_j (S^T q_j) + sum_{i<j} (D_j / D_i) KQ_ij u_i + KQ_jj u_j,
+//                              S  <- D_7 S + sum_j (D_7 / D_j) k_j u_j^T
+//                          so the sixteen dot products against S are reduced over the lanes in ONE round per block, the
+//                          dependent part is a few scalar operations per column, and the eight rank-one updates are one pass
+//                          over the registers.  A column's `dim` elements sit on LPC lanes (8 when there are columns enough to
+//                          fill the chip, else 32) so that a warp carries 32 / LPC columns; chunks of 16 tokens arrive through
+//                          a two-stage cp.async ring.  Differs from the token-serial form only by fp32 rounding.
+//   delta_gram_kernel      KK and KQ of every block of eight rows of a portion (blocks count from the portion's first row).
 //   gated_rmsnorm_heads    one warp per (row, head): o / sqrt(mean(o^2) + eps) * w * silu(gate), stored in the storage type.
 #include <cuda_bf16.h>
 
@@ -190,6 +203,236 @@ __global__ void __launch_bounds__(kScanCols * 32) delta_scan_kernel(float* out, 
   }
 }
 
+__device__ __forceinline__ void cp_async_f(float* dst, const float* src, bool valid) {
+  const uint32_t d = (uint32_t) __cvta_generic_to_shared(dst);
+  const int n = valid ? 4 : 0;                        // 0 source bytes: the destination is zero-filled
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_f4(float* dst, const float* src, bool valid) {
+  const uint32_t d = (uint32_t) __cvta_generic_to_shared(dst);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit_wait_all(bool commit) {
+  if (commit) asm volatile("cp.async.commit_group;");
+  else asm volatile("cp.async.wait_group 0;");
+}
+
+constexpr int kBlk = 8;          // tokens resolved at a time
+constexpr int kBlkChunk = 16;    // tokens per staged chunk (two blocks)
+
+// gram [rows][G][8][2]: for row j of its block and i <= j, k_i . k_j and k_i . q_j.  One CTA per (block, query / key head, sequence);
+// a dot product per group of 8 lanes.
+__global__ void __launch_bounds__(256) delta_gram_kernel(float* gram, ScanArgs a) {
+  const int e = blockIdx.z, g = blockIdx.y, t0 = blockIdx.x * kBlk;
+  const int len = a.seq_len[e], row0 = a.seq_start[e];
+  if (t0 >= len) return;
+  const int C = 2 * a.G * a.dim + a.H * a.vdim;
+  const int grp = threadIdx.x / 8, l8 = threadIdx.x % 8;
+  for (int idx = grp; idx < kBlk * kBlk * 2; idx += 32) {
+    const int kind = idx & 1, i = (idx >> 1) % kBlk, j = (idx >> 1) / kBlk;
+    const bool need = i <= j && t0 + j < len;                                // uniform over the group
+    float s_ = 0.f;
+    if (need) {
+      const float* x = a.u + (int64_t) (row0 + t0 + i) * C + (a.G + g) * a.dim;
+      const float* y = a.u + (int64_t) (row0 + t0 + j) * C + (kind ? g : a.G + g) * a.dim;
+      for (int d = l8; d < a.dim; d += 8) s_ = fmaf(x[d], y[d], s_);
+    }
+    s_ += __shfl_xor_sync(0xffffffffu, s_, 4);
+    s_ += __shfl_xor_sync(0xffffffffu, s_, 2);
+    s_ += __shfl_xor_sync(0xffffffffu, s_, 1);
+    if (need && l8 == 0) gram[(((int64_t) (row0 + t0 + j) * a.G + g) * kBlk + i) * 2 + kind] = s_;
+  }
+}
+
+// One CTA = NW warps = NW * (32 / LPC) value columns of one (sequence, head).  A thread holds DPL state elements of its column:
+// element i is dim index ((i / VEC) * LPC + sub) * VEC + i % VEC (VEC = 4 when DPL allows 16-byte shared loads), so that the
+// lanes of a column read neighbouring pieces of a staged key row.  Staged rows are LDK = LPC * DPL >= dim floats wide, zero behind dim.
+// Shared memory per stage: k [16][LDK] | q [16][LDK] | products [16][8][2] | v [16][COLS] | beta [16] | g [16].
+template <int LPC, int DPL, int NW>
+__global__ void __launch_bounds__(NW * 32) delta_scan_blocked_kernel(float* out, ScanArgs a, const float* gram, int vec4) {
+  constexpr int T = kBlk, TCH = kBlkChunk, CPW = 32 / LPC, COLS = NW * CPW, LDK = LPC * DPL, VEC = DPL % 4 == 0 ? 4 : 1, NT = NW * 32;
+  constexpr int STAGE = 2 * TCH * LDK + TCH * T * 2 + TCH * COLS + 2 * TCH;
+  extern __shared__ __align__(16) float smem[];
+  const int e = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * COLS;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, sub = lane % LPC;
+  const int cc = warp * CPW + lane / LPC, col = c0 + cc;
+  const bool live = col < a.vdim;
+  const int len = a.seq_len[e], past = a.seq_past[e], row0 = a.seq_start[e];
+  const int jh = h / (a.H / a.G);                                            // the head's query / key head
+  const int C = 2 * a.G * a.dim + a.H * a.vdim;
+  auto dmap = [&](int i) { return ((i / VEC) * LPC + sub) * VEC + i % VEC; };
+  float* sp = a.state + (((int64_t) a.seq_slot[e] * a.H + h) * a.vdim + (live ? col : 0)) * a.dim;
+  float S[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) {
+    const int d = dmap(i);
+    S[i] = (live && past > 0 && d < a.dim) ? sp[d] : 0.f;                    // a sequence at position 0 starts from zeros
+  }
+  // the padding behind dim is never written by the copies: zero it once in both stages
+  for (int i = threadIdx.x; i < 2 * STAGE; i += NT) smem[i] = 0.f;
+  __syncthreads();
+  auto stage_in = [&](int c, int buf) {
+    float* ks = smem + buf * STAGE;
+    float* qs = ks + TCH * LDK;
+    float* gr = qs + TCH * LDK;
+    float* vs = gr + TCH * T * 2;
+    float* bs = vs + TCH * COLS;
+    const int t0 = c * TCH, nt = min(TCH, len - t0);
+    const float* ub = a.u + (int64_t) (row0 + t0) * C;
+    if (vec4) {
+      const int per = a.dim / 4;
+      for (int i = threadIdx.x; i < TCH * per; i += NT) {
+        const int t = i / per, d = (i % per) * 4;
+        const bool ok = t < nt;
+        cp_async_f4(qs + t * LDK + d, ok ? ub + (int64_t) t * C + jh * a.dim + d : a.u, ok);
+        cp_async_f4(ks + t * LDK + d, ok ? ub + (int64_t) t * C + (a.G + jh) * a.dim + d : a.u, ok);
+      }
+    } else {
+      for (int i = threadIdx.x; i < TCH * a.dim; i += NT) {
+        const int t = i / a.dim, d = i % a.dim;
+        const bool ok = t < nt;
+        cp_async_f(qs + t * LDK + d, ok ? ub + (int64_t) t * C + jh * a.dim + d : a.u, ok);
+        cp_async_f(ks + t * LDK + d, ok ? ub + (int64_t) t * C + (a.G + jh) * a.dim + d : a.u, ok);
+      }
+    }
+    for (int i = threadIdx.x; i < TCH * COLS; i += NT) {
+      const int t = i / COLS, c_ = c0 + i % COLS;
+      const bool ok = t < nt && c_ < a.vdim;
+      cp_async_f(vs + i, ok ? ub + (int64_t) t * C + 2 * a.G * a.dim + h * a.vdim + c_ : a.u, ok);
+    }
+    for (int i = threadIdx.x; i < TCH * (T * 2 / 4); i += NT) {              // a row's products: 16 floats, 16-byte aligned
+      const int t = i / (T * 2 / 4), p4 = (i % (T * 2 / 4)) * 4;
+      const bool ok = t < nt;
+      cp_async_f4(gr + t * T * 2 + p4, ok ? gram + ((int64_t) (row0 + t0 + t) * a.G + jh) * T * 2 + p4 : gram, ok);
+    }
+    for (int i = threadIdx.x; i < 2 * TCH; i += NT) {
+      const int t = i % TCH, which = i / TCH;                                // beta, then g
+      const bool ok = t < nt;
+      cp_async_f(bs + i, ok ? a.bg + (int64_t) (row0 + t0 + t) * 2 * a.H + which * a.H + h : a.bg, ok);
+    }
+    cp_async_commit_wait_all(true);
+  };
+  const int nch = (len + TCH - 1) / TCH;
+  if (nch > 0) stage_in(0, 0);
+  for (int c = 0; c < nch; ++c) {
+    // behind this barrier chunk c has landed (every thread waited for its own copies) and every warp has left the other stage
+    cp_async_commit_wait_all(false);
+    __syncthreads();
+    if (c + 1 < nch) stage_in(c + 1, (c + 1) & 1);
+    const float* ks = smem + (c & 1) * STAGE;
+    const float* qs = ks + TCH * LDK;
+    const float* gr = qs + TCH * LDK;
+    const float* vs = gr + TCH * T * 2;
+    const float* bs = vs + TCH * COLS;
+    const float* gs = bs + TCH;
+    const int t0 = c * TCH;
+#pragma unroll 1
+    for (int b = 0; b < TCH / T; ++b) {
+      const int tb = t0 + b * T;
+      if (tb >= len) break;
+      const float* kb = ks + b * T * LDK;
+      const float* qb = qs + b * T * LDK;
+      float A[T], B[T];
+#pragma unroll
+      for (int j = 0; j < T; ++j) {
+        float pa = 0.f, pb = 0.f;
+        if constexpr (VEC == 4) {
+#pragma unroll
+          for (int v4 = 0; v4 < DPL / 4; ++v4) {
+            const float4 kv = *reinterpret_cast<const float4*>(kb + j * LDK + (v4 * LPC + sub) * 4);
+            const float4 qv = *reinterpret_cast<const float4*>(qb + j * LDK + (v4 * LPC + sub) * 4);
+            pa = fmaf(S[4 * v4], kv.x, pa); pa = fmaf(S[4 * v4 + 1], kv.y, pa); pa = fmaf(S[4 * v4 + 2], kv.z, pa); pa = fmaf(S[4 * v4 + 3], kv.w, pa);
+            pb = fmaf(S[4 * v4], qv.x, pb); pb = fmaf(S[4 * v4 + 1], qv.y, pb); pb = fmaf(S[4 * v4 + 2], qv.z, pb); pb = fmaf(S[4 * v4 + 3], qv.w, pb);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < DPL; ++i) {
+            pa = fmaf(S[i], kb[j * LDK + dmap(i)], pa);
+            pb = fmaf(S[i], qb[j * LDK + dmap(i)], pb);
+          }
+        }
+        A[j] = pa;
+        B[j] = pb;
+      }
+#pragma unroll
+      for (int o = LPC / 2; o > 0; o >>= 1) {
+#pragma unroll
+        for (int j = 0; j < T; ++j) {
+          A[j] += __shfl_xor_sync(0xffffffffu, A[j], o);
+          B[j] += __shfl_xor_sync(0xffffffffu, B[j], o);
+        }
+      }
+      // the dependent part, per column: ut[i] = u_i * (D_j / D_i) as j advances
+      const float* pr = gr + b * T * T * 2;                                 // [j][i][kk, kq]
+      float ut[T], D = 1.f;
+#pragma unroll
+      for (int j = 0; j < T; ++j) {
+        const bool in = tb + j < len;
+        const float g = in ? gs[b * T + j] : 1.f;                            // a token behind the portion's end changes nothing
+        D *= g;
+        float aj = D * A[j], oj = D * B[j];
+#pragma unroll
+        for (int i = 0; i < j; ++i) {
+          ut[i] *= g;
+          aj = fmaf(pr[(j * T + i) * 2], ut[i], aj);
+          oj = fmaf(pr[(j * T + i) * 2 + 1], ut[i], oj);
+        }
+        const float uj = in ? bs[b * T + j] * (vs[(b * T + j) * COLS + cc] - aj) : 0.f;
+        ut[j] = uj;
+        oj = fmaf(pr[(j * T + j) * 2 + 1], uj, oj);
+        if (in && live && sub == 0) out[((int64_t) (row0 + tb + j) * a.H + h) * a.vdim + col] = oj;
+      }
+      if constexpr (VEC == 4) {
+#pragma unroll
+        for (int v4 = 0; v4 < DPL / 4; ++v4) {
+          float s0 = D * S[4 * v4], s1 = D * S[4 * v4 + 1], s2 = D * S[4 * v4 + 2], s3 = D * S[4 * v4 + 3];
+#pragma unroll
+          for (int j = 0; j < T; ++j) {
+            const float4 kv = *reinterpret_cast<const float4*>(kb + j * LDK + (v4 * LPC + sub) * 4);
+            s0 = fmaf(ut[j], kv.x, s0); s1 = fmaf(ut[j], kv.y, s1); s2 = fmaf(ut[j], kv.z, s2); s3 = fmaf(ut[j], kv.w, s3);
+          }
+          S[4 * v4] = s0; S[4 * v4 + 1] = s1; S[4 * v4 + 2] = s2; S[4 * v4 + 3] = s3;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+          float acc = D * S[i];
+#pragma unroll
+          for (int j = 0; j < T; ++j) acc = fmaf(ut[j], kb[j * LDK + dmap(i)], acc);
+          S[i] = acc;
+        }
+      }
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      const int d = dmap(i);
+      if (d < a.dim) sp[d] = S[i];
+    }
+  }
+}
+
+template <int LPC, int DPL, int NW>
+int launch_scan_blocked(float* out, const ScanArgs& a, float* gram, int seqs, int max_len, cudaStream_t s) {
+  constexpr int COLS = NW * (32 / LPC), LDK = LPC * DPL;
+  constexpr size_t smem = (size_t) 2 * (2 * kBlkChunk * LDK + kBlkChunk * kBlk * 2 + kBlkChunk * COLS + 2 * kBlkChunk) * sizeof(float);
+  static bool raised = false;
+  if (!raised && smem > 48 * 1024) {
+    TB_CHECK_CUDA(cudaFuncSetAttribute(delta_scan_blocked_kernel<LPC, DPL, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    raised = true;
+  }
+  delta_gram_kernel<<<dim3((max_len + kBlk - 1) / kBlk, a.G, seqs), 256, 0, s>>>(gram, a);
+  TB_CHECK_CUDA(cudaGetLastError());
+  const int C = 2 * a.G * a.dim + a.H * a.vdim;
+  const int vec4 = a.dim % 4 == 0 && C % 4 == 0 && LDK % 4 == 0 && (uintptr_t) a.u % 16 == 0;
+  dim3 grid((a.vdim + COLS - 1) / COLS, a.H, seqs);
+  delta_scan_blocked_kernel<LPC, DPL, NW><<<grid, NW * 32, smem, s>>>(out, a, gram, vec4);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) gated_rmsnorm_heads_kernel(T* out, const float* o, const float* gate, int64_t ldg, const void* w,
                                                                   int w_dtype, float eps, int64_t items, int H, int vdim) {
@@ -250,13 +493,28 @@ extern "C" int tb_delta_prepare(float* u, float* bg, const float* proj, int64_t 
 
 extern "C" int tb_delta_rule_scan(float* out, const float* u, const float* bg, float* state, const int* seq_start, const int* seq_len,
                                   const int* seq_past, const int* seq_slot, int seqs, int heads, int kv_heads, int dim, int vdim,
-                                  tb_stream_t stream) {
+                                  int max_len, float* workspace, tb_stream_t stream) {
   if (!out || !u || !bg || !state || !seq_start || !seq_len || !seq_past || !seq_slot) return -1;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || dim > 512 || vdim <= 0 || seqs < 0 || seqs > 65535 || heads > 65535)
     return -1;
   if (seqs == 0) return 0;
   ScanArgs a{u, bg, state, seq_start, seq_len, seq_past, seq_slot, heads, kv_heads, dim, vdim};
   cudaStream_t s = (cudaStream_t) stream;
+  if (max_len >= 3 && workspace) {
+    // prompt portions: eight tokens at a time; a column on 8 lanes when that still gives the chip warps enough
+    const bool narrow = (int64_t) seqs * heads * vdim >= 1200 && dim <= 128;
+    const int ldk = dim <= 32 ? 32 : dim <= 64 ? 64 : dim <= 128 ? 128 : dim <= 256 ? 256 : 512;
+    if (narrow) {
+      if (ldk == 32) return launch_scan_blocked<8, 4, 4>(out, a, workspace, seqs, max_len, s);
+      if (ldk == 64) return launch_scan_blocked<8, 8, 4>(out, a, workspace, seqs, max_len, s);
+      return launch_scan_blocked<8, 16, 4>(out, a, workspace, seqs, max_len, s);
+    }
+    if (ldk == 32) return launch_scan_blocked<32, 1, 8>(out, a, workspace, seqs, max_len, s);
+    if (ldk == 64) return launch_scan_blocked<32, 2, 8>(out, a, workspace, seqs, max_len, s);
+    if (ldk == 128) return launch_scan_blocked<32, 4, 8>(out, a, workspace, seqs, max_len, s);
+    if (ldk == 256) return launch_scan_blocked<32, 8, 8>(out, a, workspace, seqs, max_len, s);
+    return launch_scan_blocked<32, 16, 8>(out, a, workspace, seqs, max_len, s);
+  }
   const int dpl = (dim + 31) / 32;
   if (dpl <= 1) return launch_scan<1>(out, a, seqs, s);
   if (dpl <= 2) return launch_scan<2>(out, a, seqs, s);

@@ -525,7 +525,7 @@ int launch_window_mma(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_bfl
 }
 
 // the (dim, vdim) pairs the tensor-core kernel is built for
-#define TB_WINDOW_MMA_SHAPES(X) X(32, 16) X(32, 32) X(64, 32) X(64, 64) X(96, 96) X(128, 64) X(128, 128)
+#define TB_WINDOW_MMA_SHAPES(X) X(32, 16) X(32, 32) X(64, 32) X(64, 64) X(64, 128) X(96, 96) X(128, 64) X(128, 128)
 
 }  // namespace
 }  // namespace tb

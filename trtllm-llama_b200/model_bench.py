@@ -1,6 +1,7 @@
-"""``bench.py --model zobasun | nililix``: prefill and decode throughput of an in-flight served design at layer sizes that
-resemble real models (random bf16 weights), beside a LLaMA engine of equal width / depth / feed-forward size served by
-``GenerationSession`` (fp16), and every operator's distance from its roofline.
+"""``bench.py --model zobasun | nililix | mimolix``: prefill and decode throughput of an in-flight served design at layer
+sizes that resemble real models (random bf16 weights), beside a LLaMA engine of equal width / depth / feed-forward size
+served by ``GenerationSession`` (fp16) — for Mimolix beside Nililix, the closest in-flight design, at equal size — and every
+operator's distance from its roofline.
 
 Timing: CUDA events on the launching stream, >= 3 warm-up runs; every timed run works on tensors far larger than L2 or is
 preceded by an L2 flush (a 256 MB fill).  Whole steps are timed from an idle device (synchronise, then the start event);
@@ -99,13 +100,62 @@ def random_nililix(torch, s, seed=0):
     return cfg, t
 
 
+MIMOLIX_SIZES = {
+    # differential attention: heads x (2 maps of dim) over kv_heads, values of vdim; delta rule: heads x vdim over kv_heads x dim;
+    # feed-forward: `experts` experts of eff with `top` active plus a shared expert of eff
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=64, vdim=128, d_heads=16, d_kv_heads=4, d_dim=128, d_vdim=128, experts=16,
+                  top=4, eff=1408, ff=5632, vocab=32000),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=64, vdim=128, d_heads=32, d_kv_heads=8, d_dim=128, d_vdim=128, experts=16,
+                  top=4, eff=2752, ff=11008, vocab=32000),
+}
+
+
+def random_mimolix(torch, s, seed=0):
+    """config + bf16 tensors of a 4-layer stack [delta, attention, delta, attention] whose middle two layers run twice; every
+    layer with routed experts and a shared expert."""
+    g = torch.Generator().manual_seed(seed)
+    W, H, G, d, dv = s["width"], s["heads"], s["kv_heads"], s["dim"], s["vdim"]
+    DH, DG, dd, ddv = s["d_heads"], s["d_kv_heads"], s["d_dim"], s["d_vdim"]
+
+    def n(*shape, std=None):
+        std = std if std is not None else shape[-1] ** -0.5
+        return (torch.randn(*shape, generator=g) * std).to(torch.bfloat16)
+
+    att = dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=d ** -0.5, diff=0.5, q_temp=dict(coef=0.5, every=1024))
+    dlt = dict(heads=DH, kv_heads=DG, dim=dd, vdim=ddv, conv=4)
+    moe = dict(kind="moe", expert=dict(ff=s["eff"]), router=dict(experts=s["experts"], top=s["top"], scale=2.0), shared=dict(ff=s["eff"]))
+    layers = [dict(type=ty, mixer=dict(att if ty == "attention" else dlt), mlp=moe) for ty in ("delta", "attention", "delta", "attention")]
+    cfg = dict(architecture="Mimolix", vocab=s["vocab"], width=W, embedding=dict(scale=1.0), norm=dict(eps=1e-6), residual_mult=0.7,
+               loop=dict(start=1, stop=3, times=2), layers=layers)
+    t = {"embed": n(s["vocab"], W, std=1.0), "head": n(s["vocab"], W), "final.norm": n(W, std=0.1) + 1, "final.norm.b": n(W, std=0.1),
+         "loop.in": n(W, 2 * W)}
+    for i, l in enumerate(layers):
+        p = f"l{i}."
+        t[p + "norm1"], t[p + "norm1.b"] = n(W, std=0.1) + 1, n(W, std=0.1)
+        if l["type"] == "attention":
+            t.update({p + "mix.q": n(H * 2 * d, W), p + "mix.k": n(G * 2 * d, W), p + "mix.v": n(G * dv, W), p + "mix.q.norm": n(d, std=0.1) + 1,
+                      p + "mix.k.norm": n(d, std=0.1) + 1, p + "mix.o": n(W, H * dv)})
+            for k in ("lq1", "lk1", "lq2", "lk2"):
+                t[p + "mix." + k] = n(d, std=0.1)
+        else:
+            t.update({p + "mix.q": n(DG * dd, W), p + "mix.k": n(DG * dd, W), p + "mix.v": n(DH * ddv, W), p + "mix.q.conv": n(DG * dd, 4, std=0.5),
+                      p + "mix.k.conv": n(DG * dd, 4, std=0.5), p + "mix.v.conv": n(DH * ddv, 4, std=0.5), p + "mix.b": n(DH, W),
+                      p + "mix.a": n(DH, W), p + "mix.A_log": n(DH, std=0.5) - 2, p + "mix.dt_bias": n(DH, std=0.5), p + "mix.norm": n(ddv, std=0.1) + 1,
+                      p + "mix.g": n(DH * ddv, W), p + "mix.o": n(W, DH * ddv)})
+        t.update({p + "mlp.router": n(s["experts"], W), p + "mlp.shared.up": n(s["eff"], W), p + "mlp.shared.down": n(W, s["eff"])})
+        for e in range(s["experts"]):
+            t.update({f"{p}mlp.e{e}.up": n(s["eff"], W), f"{p}mlp.e{e}.down": n(W, s["eff"])})
+    return cfg, t
+
+
 class OpTimer:
     """Wraps the ragged operators of ``ops`` with CUDA-event timers and the bytes / flops each call moves."""
 
     NAMES = ("linear", "linear_gated", "embed_scaled", "rmsnorm_rows", "gated_act", "rope_table", "rope_query_tail", "latent_kv_append",
              "latent_attention", "causal_conv1d", "rglru_scan", "qkv_conv_rope_append", "window_attention", "moe_route",
              "moe_plan", "moe_linear", "moe_linear_tc", "moe_gemv", "moe_gather_rows", "moe_combine", "add_row_vector", "tanh_cap",
-             "residual_norm_rows")
+             "residual_norm_rows", "layernorm_rows", "residual_layernorm_rows", "concat_rows", "qk_norm_append", "diff_combine",
+             "delta_prepare", "delta_rule_scan", "gated_rmsnorm_heads", "moe_route_softmax")
 
     def __init__(self, torch, ops):
         self.torch, self.ops, self.rec, self.saved = torch, ops, [], {}
@@ -142,6 +192,7 @@ class OpTimer:
         if name == "window_attention":
             q, pool, batch, page, G, dv, window = args[0], args[1], args[2], args[3], args[4], args[5], args[7]
             H, d = q.shape[1], q.shape[2]
+            vsh = kw.get("v_share", 1)
             pos = batch._host[batch.num_rows * 2:batch.num_rows * 3].double()
             keys = float(((pos + 1).clamp(max=window) if window else (pos + 1)).sum())
             seq = batch._host[batch.num_rows:batch.num_rows * 2].tolist()
@@ -151,7 +202,7 @@ class OpTimer:
                 last[sq] = max(last.get(sq, p), p)
             # minimal traffic: the cached positions any row of the sequence sees, once; queries and outputs once
             seen = sum(last[sq] + 1 - (max(0, first[sq] - window + 1) if window else 0) for sq in first)
-            return name, 2.0 * keys * H * (d + dv), seen * G * (d + dv) * pool.element_size() + nb(q, out)
+            return name, 2.0 * keys * H * (d + dv), seen * (G * d + G // vsh * dv) * pool.element_size() + nb(q, out)
         if name == "qkv_conv_rope_append":
             proj, H, G, d, dv = args[0], args[8], args[9], args[10], args[11]
             C = H * d + G * (d + dv)
@@ -159,6 +210,18 @@ class OpTimer:
         if name == "moe_route":
             self._pairs = args[0].shape[0] * args[2]            # rows * top: the pairs the expert products below work on
             return name, 0.0, nb(args[0], *out)
+        if name == "moe_route_softmax":
+            self._pairs = args[0].shape[0] * args[1]
+            return name, 0.0, nb(args[0], *out)
+        if name == "delta_rule_scan":
+            u, bg, state, batch, H, G, d, dv = args
+            # the state of every sequence in the step is read and written once; rows in and out once
+            return name, 6.0 * u.shape[0] * H * d * dv, nb(u, bg, out) + 2 * batch.num_seqs * H * d * dv * 4
+        if name == "delta_prepare":
+            return name, 0.0, args[0].shape[0] * (2 * kw.get("C", args[8] * args[11] + 2 * args[9] * args[10]) * 4) + nb(*out[1:])
+        if name == "qk_norm_append":
+            proj, pool, qv, kv, d, vc = args[0], args[4], args[7], args[8], args[9], args[10]
+            return name, 0.0, proj.shape[0] * ((qv + kv) * d + vc) * (4 + pool.element_size())
         if name in ("moe_linear", "moe_linear_tc", "moe_gemv"):
             a, w = args[0], args[1]
             if out is None:
@@ -458,13 +521,133 @@ def bench_nililix_size(torch, name, steps, warmup, S=2048, B=4):
     return res
 
 
+def _serve(torch, ops, model, vocab, S, B, steps, warmup, flush, peaks):
+    """Prefill of one S-token prompt in one step and generation steps of B sequences at context S through ``InflightSession``,
+    with every operator timed once on eager launches."""
+    from .inflight import InflightSession
+    sess = InflightSession(model, max_tokens=(B + 1) * (S + 64), max_seqs=B + 1)
+    prompt = torch.randint(0, vocab, (S,), generator=torch.Generator().manual_seed(1)).tolist()
+    res = {}
+
+    def prefill():
+        sess.step([("p", prompt, [S - 1])])
+        sess.end("p")
+    t = _time(torch, prefill, steps, warmup, flush)
+    res["prefill_tokens_per_s"] = round(S / t, 1)
+    res["prefill_ms"] = round(t * 1e3, 3)
+    with OpTimer(torch, ops) as ot:
+        prefill()
+    res["prefill_ops"] = ot.summary(peaks)
+    for b in range(B):
+        sess.step([(("d", b), prompt, [])])
+    dec = [(("d", b), [7 + b], [0]) for b in range(B)]
+    t = _time(torch, lambda: sess.step(dec), steps, warmup, flush)
+    res["decode_tokens_per_s"] = round(B / t, 1)
+    res["decode_ms_per_step"] = round(t * 1e3, 3)
+    sess.use_cuda_graph = False          # the operators are timed one by one on eager launches
+    with OpTimer(torch, ops) as ot:
+        sess.step(dec)
+    res["decode_ops"] = ot.summary(peaks)
+    t = _time(torch, lambda: sess.step(dec), steps, warmup, flush)
+    res["decode_ms_per_step_eager"] = round(t * 1e3, 3)
+    return res
+
+
+def bench_mimolix_size(torch, name, steps, warmup, S=2048, B=4):
+    """Mimolix beside Nililix (the closest design served in-flight: grouped-query attention, routed experts, a looped block) at
+    equal width, heads, expert sizes, vocabulary and number of layer runs; then the like kernels alone on the same shapes:
+    differential against windowed attention, the delta rule against the gated linear recurrence, the fused residual steps."""
+    from . import ops
+    from .inflight import RaggedBatch
+    from .models.mimolix import build_mimolix
+    from .models.nililix import build_nililix
+    s, peaks = MIMOLIX_SIZES[name], _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    cfg, tensors = random_mimolix(torch, s)
+    model = build_mimolix(cfg, tensors, torch.bfloat16, "cuda")
+    del tensors
+    res = {"size": dict(s), "layers": [l["type"] for l in cfg["layers"]], "layer_runs": len(model.runs), "prefill_tokens": S,
+           "decode_batch": B, "decode_context": S}
+    res["mimolix"] = _serve(torch, ops, model, s["vocab"], S, B, steps, warmup, flush, peaks)
+    del model
+    torch.cuda.empty_cache()
+    ns = dict(NILILIX_SIZES[name], window=0)          # all keys visible, as here
+    ncfg, ntensors = random_nililix(torch, ns)
+    nmodel = build_nililix(ncfg, ntensors, torch.bfloat16, "cuda")
+    del ntensors
+    res["nililix"] = _serve(torch, ops, nmodel, ns["vocab"], S, B, steps, warmup, flush, peaks)
+    res["nililix"]["layers"] = [l["mlp"]["kind"] for l in ncfg["layers"]]
+    del nmodel
+    torch.cuda.empty_cache()
+
+    like = {}
+    H, G, d, dv, page = s["heads"], s["kv_heads"], s["dim"], s["vdim"], 64
+    nblk = -(-S // page)
+    pb = RaggedBatch([([0] * S, 0, 0, list(range(nblk)))], [], "cuda")
+    db = RaggedBatch([([0], S - 1, b, list(range(b * nblk, (b + 1) * nblk))) for b in range(B)], [], "cuda")
+    keys = S * (S + 1) / 2
+    # differential attention: 2 H (head, map) queries of d against 2 G key heads, G value heads
+    pool = torch.randn((B * nblk * page, G * (2 * d + dv)), device="cuda").bfloat16()
+    q = torch.randn(S, 2 * H, d, device="cuda").bfloat16()
+    t = _time_kernel(torch, lambda: ops.window_attention(q, pool, pb, page, 2 * G, dv, 0.1, 0, v_share=2, out_f32=True), steps, warmup, flush)
+    like["differential_attention_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(2.0 * keys * 2 * H * (d + dv) / (peaks["bf16_tflops"] * 1e12) / t, 3)}
+    qd = q[:B].contiguous()
+    t = _time_kernel(torch, lambda: ops.window_attention(qd, pool, db, page, 2 * G, dv, 0.1, 0, v_share=2, out_f32=True), steps, warmup, flush)
+    cb = B * S * G * (2 * d + dv) * 2
+    like["differential_attention_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(cb / (peaks["hbm_gbs"] * 1e9) / t, 3), "cache_bytes": cb}
+    # Nililix' attention on its own shapes, all keys visible
+    NH, NG, nd, ndv = ns["heads"], ns["kv_heads"], ns["dim"], ns["vdim"]
+    npool = torch.randn((B * nblk * page, NG * (nd + ndv)), device="cuda").bfloat16()
+    nq = torch.randn(S, NH, nd, device="cuda").bfloat16()
+    t = _time_kernel(torch, lambda: ops.window_attention(nq, npool, pb, page, NG, ndv, 0.1, 0), steps, warmup, flush)
+    like["nililix_attention_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(2.0 * keys * NH * (nd + ndv) / (peaks["bf16_tflops"] * 1e12) / t, 3)}
+    nqd = nq[:B].contiguous()
+    t = _time_kernel(torch, lambda: ops.window_attention(nqd, npool, db, page, NG, ndv, 0.1, 0), steps, warmup, flush)
+    cb = B * S * NG * (nd + ndv) * 2
+    like["nililix_attention_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(cb / (peaks["hbm_gbs"] * 1e9) / t, 3), "cache_bytes": cb}
+    del pool, npool, q, nq
+    # the recurrences: delta rule (matrix state per head) against the gated linear recurrence (vector state) of equal width
+    DH, DG, dd, ddv = s["d_heads"], s["d_kv_heads"], s["d_dim"], s["d_vdim"]
+    C = 2 * DG * dd + DH * ddv
+    u, bg = torch.randn(S, C, device="cuda") * 0.05, torch.rand(S, 2 * DH, device="cuda")
+    state = torch.zeros(B + 1, DH * ddv * dd, device="cuda")
+    t = _time_kernel(torch, lambda: ops.delta_rule_scan(u, bg, state, pb, DH, DG, dd, ddv), steps, warmup, flush)
+    by = (u.numel() + bg.numel() + S * DH * ddv) * 4 + 2 * DH * dd * ddv * 4
+    like["delta_rule_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(by / (peaks["hbm_gbs"] * 1e9) / t, 3),
+                                  "fp32_tflops": round(6.0 * S * DH * dd * ddv / t / 1e12, 2)}
+    ud, bgd = u[:B].contiguous(), bg[:B].contiguous()
+    t = _time_kernel(torch, lambda: ops.delta_rule_scan(ud, bgd, state, db, DH, DG, dd, ddv), steps, warmup, flush)
+    by = 2 * B * DH * dd * ddv * 4
+    like["delta_rule_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(by / (peaks["hbm_gbs"] * 1e9) / t, 3), "state_bytes": by}
+    Cr, blocks = s["width"], s["width"] // 128
+    ur, gates = torch.randn(S, Cr, device="cuda"), torch.randn(S, blocks, 2 * (Cr // blocks), device="cuda")
+    lam, y = torch.randn(Cr, device="cuda").bfloat16(), torch.randn(S, Cr, device="cuda").bfloat16()
+    rstate = torch.zeros(B + 1, Cr, device="cuda")
+    t = _time_kernel(torch, lambda: ops.rglru_scan(ur, gates, lam, y, rstate, pb, blocks, 8.0), steps, warmup, flush)
+    by = ur.numel() * 4 + gates.numel() * 4 + 2 * y.numel() * 2
+    like["gated_linear_recurrence_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(by / (peaks["hbm_gbs"] * 1e9) / t, 3)}
+    # residual step + next norm: parallel layers' layer norm against the sandwich RMS norms
+    W = s["width"]
+    x, y1, y2 = (torch.randn(S, W, device="cuda") for _ in range(3))
+    w, b = torch.ones(W, device="cuda").bfloat16(), torch.zeros(W, device="cuda").bfloat16()
+    t = _time_kernel(torch, lambda: ops.residual_layernorm_rows(x, y1, y2, 0.7, w, b, 1e-6, torch.bfloat16), steps, warmup, flush)
+    like["residual_layernorm"] = {"us": round(t * 1e6, 1), "of_roofline": round(S * W * (4 * 4 + 2) / (peaks["hbm_gbs"] * 1e9) / t, 3)}
+    t = _time_kernel(torch, lambda: ops.residual_norm_rows(x, y1, w, w, 1e-6, 0.0, 0.7, torch.bfloat16), steps, warmup, flush)
+    like["nililix_residual_norm"] = {"us": round(t * 1e6, 1), "of_roofline": round(S * W * (3 * 4 + 2) / (peaks["hbm_gbs"] * 1e9) / t, 3)}
+    res["like_kernels"] = like
+    res["peaks"] = peaks
+    torch.cuda.empty_cache()
+    return res
+
+
 def run(args):
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("bench.py --model needs a B200 (sm_100a): there is no CPU path")
-    sizes, fn = (NILILIX_SIZES, bench_nililix_size) if args.model == "nililix" else (SIZES, bench_size)
+    sizes, fn = {"nililix": (NILILIX_SIZES, bench_nililix_size), "mimolix": (MIMOLIX_SIZES, bench_mimolix_size),
+                 "zobasun": (SIZES, bench_size)}[args.model]
     names = args.model_sizes.split(",") if args.model_sizes else list(sizes)
-    out = {"bench": "model_compare", "model": args.model, "dtype": "bf16 (llama: fp16)", "data": "synthetic",
+    out = {"bench": "model_compare", "model": args.model, "dtype": "bf16" if args.model == "mimolix" else "bf16 (llama: fp16)", "data": "synthetic",
            "steps": args.steps, "warmup": max(3, args.warmup), "sizes": {}}
     for nm in names:
         out["sizes"][nm] = fn(torch, nm, args.steps, args.warmup)

@@ -351,6 +351,7 @@ TC_MIN_ROWS = 17
 # the tile kernel instead of the streaming GEMV
 FORCE_SIMT_ATTENTION = False
 FORCE_TILE_LINEAR = False
+FORCE_SERIAL_SCAN = False      # A/B: the delta rule row by row also for prompt portions
 COMPUTE_TILES = 2
 
 
@@ -679,8 +680,12 @@ def delta_rule_scan(u, bg, state, batch, heads, kv_heads, dim, vdim):
     """The gated delta rule over every sequence's rows, from and into ``state`` (fp32 [slots, heads * vdim * dim])."""
     _chk_cuda(u, bg, state)
     out = torch.empty((u.shape[0], heads, vdim), dtype=torch.float32, device=u.device)
+    ws = None
+    if batch.max_len >= 3 and not FORCE_SERIAL_SCAN:      # prompt portions: eight rows at a time over the blocks' own k.k and k.q products
+        ws = torch.empty((u.shape[0], kv_heads, 16), dtype=torch.float32, device=u.device)
     check(_rl.tb_delta_rule_scan(_p(out), _p(u), _p(bg), _p(state), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
-                                 _p(batch.seq_slot), batch.num_seqs, heads, kv_heads, dim, vdim, _stream()), "tb_delta_rule_scan")
+                                 _p(batch.seq_slot), batch.num_seqs, heads, kv_heads, dim, vdim, batch.max_len, _p(ws), _stream()),
+          "tb_delta_rule_scan")
     return out
 
 
