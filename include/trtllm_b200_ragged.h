@@ -242,12 +242,12 @@ int tb_delta_prepare(float* u, float* bg, const float* proj, int64_t ldp, const 
                      int kv_heads, int dim, int vdim, int taps, float eps_unit, tb_stream_t stream);
 /* The recurrence over every sequence's rows in order, from state[slot] (fp32 [slots, heads, vdim, dim]: S transposed, a value
  * column's elements contiguous; zeros at a sequence's first position) and back into it.  out fp32 [N, heads, vdim].  dim <= 512.
- * max_len: the longest seq_len (host).  With workspace (fp32 [N, kv_heads, 16], 16-byte aligned) and max_len >= 3 the rows of a
- * sequence are resolved eight at a time (one reduction round per eight rows; the same recurrence up to fp32 rounding);
- * otherwise row by row. */
+ * rows = N; max_len: the longest seq_len (host).  With workspace (fp32, rows * (16 kv_heads + 20 heads) values, 16-byte aligned)
+ * and max_len >= 3 the rows of a sequence are resolved eight at a time (one reduction round per eight rows; the same recurrence
+ * up to fp32 rounding); otherwise row by row. */
 int tb_delta_rule_scan(float* out, const float* u, const float* bg, float* state, const int* seq_start, const int* seq_len,
-                       const int* seq_past, const int* seq_slot, int seqs, int heads, int kv_heads, int dim, int vdim, int max_len,
-                       float* workspace, tb_stream_t stream);
+                       const int* seq_past, const int* seq_slot, int rows, int seqs, int heads, int kv_heads, int dim, int vdim,
+                       int max_len, float* workspace, tb_stream_t stream);
 /* out T [N, heads, vdim] = o / sqrt(mean_vdim(o^2) + eps) * w * silu(gate): o fp32 [N, heads, vdim]; w [vdim] shared by the heads
  * (NULL: none); gate fp32 logits [N, >= heads * vdim] with row stride ldg (NULL: none). */
 int tb_gated_rmsnorm_heads(void* out, int dtype, const float* o, const float* gate, int64_t ldg, const void* w, int w_dtype, float eps,

@@ -19,12 +19,17 @@
 //                          KK_ij = k_i . k_j, KQ_ij = k_i . q_j (i <= j; delta_gram_kernel computes them once per query / key head):
 //                              a_j = D_j (S^T k_j) + sum_{i<j} (D_j / D_i) KK_ij u_i,    u_j = beta_j (v_j - a_j),
 //                              o_j = D_j (S^T q_j) + sum_{i<j} (D_j / D_i) KQ_ij u_i + KQ_jj u_j,
-//                              S  <- D_7 S + sum_j (D_7 / D_j) k_j u_j^T
-//                          so the sixteen dot products against S are reduced over the lanes in ONE round per block, the
-//                          dependent part is a few scalar operations per column, and the eight rank-one updates are one pass
-//                          over the registers.  A column's `dim` elements sit on LPC lanes (8 when there are columns enough to
-//                          fill the chip, else 32) so that a warp carries 32 / LPC columns; chunks of 16 tokens arrive through
-//                          a two-stage cp.async ring.  Differs from the token-serial form only by fp32 rounding.
+//                              S  <- D_7 S + sum_j (D_7 / D_j) k_j u_j^T.
+//                          The u_j of a block solve a triangular system whose matrix is the same for every value column,
+//                          (I + diag(beta) L) u = diag(beta) r with L_ji = (D_j / D_i) KK_ij (i < j) and r_j = v_j - D_j (S^T k_j),
+//                          so delta_block_matrices_kernel inverts it once per (block, head): M = (I + diag(beta) L)^-1 diag(beta),
+//                          W_ji = (D_j / D_i) KQ_ij.  Per column then u = M r and o = D (S^T q) + W u are short products without
+//                          a dependent chain, the sixteen dot products against S are reduced over the lanes in ONE round per
+//                          block, and the eight rank-one updates are one pass over the registers.  One warp per value column,
+//                          chunks of 16 tokens through a two-stage cp.async ring.  Differs from the token-serial form only by
+//                          fp32 rounding.
+//   delta_scan_tiled_kernel    the same with FOUR columns per warp (steps with columns enough to fill the chip): see its comment.
+//   delta_block_matrices_kernel   M, W, D_j and D_last / D_j per (block, head), one thread each.
 //   delta_gram_kernel      KK and KQ of every block of eight rows of a portion (blocks count from the portion's first row).
 //   gated_rmsnorm_heads    one warp per (row, head): o / sqrt(mean(o^2) + eps) * w * silu(gate), stored in the storage type.
 #include <cuda_bf16.h>
@@ -245,14 +250,70 @@ __global__ void __launch_bounds__(256) delta_gram_kernel(float* gram, ScanArgs a
   }
 }
 
+constexpr int kMatRow = 20;      // floats per (row, head): M_j. [8] | W_j. [8] | D_j | D_last / D_j | pad
+
+// mats [rows][H][20]; one thread per (block of 8 rows, head, sequence).  R_ji = D_j / D_i is kept as a running product (no division).
+__global__ void __launch_bounds__(128) delta_block_matrices_kernel(float* mats, const float* gram, ScanArgs a, int nblk, int seqs) {
+  constexpr int T = kBlk;
+  const int64_t id = (int64_t) blockIdx.x * 128 + threadIdx.x;
+  if (id >= (int64_t) seqs * a.H * nblk) return;
+  const int blk = (int) (id % nblk), h = (int) ((id / nblk) % a.H), e = (int) (id / ((int64_t) nblk * a.H));
+  const int len = a.seq_len[e], row0 = a.seq_start[e], t0 = blk * T;
+  if (t0 >= len) return;
+  const int nv = min(T, len - t0), g = h / (a.H / a.G);
+  float beta[T], dec[T], D[T], N[T][T], R[T][T];
+#pragma unroll
+  for (int j = 0; j < T; ++j) {
+    const bool in = j < nv;
+    beta[j] = in ? a.bg[(int64_t) (row0 + t0 + j) * 2 * a.H + h] : 0.f;
+    dec[j] = in ? a.bg[(int64_t) (row0 + t0 + j) * 2 * a.H + a.H + h] : 1.f;
+    D[j] = j ? D[j - 1] * dec[j] : dec[j];
+  }
+#pragma unroll
+  for (int j = 0; j < T; ++j) {
+    const float* gj = gram + ((int64_t) (row0 + t0 + (j < nv ? j : 0)) * a.G + g) * T * 2;      // [i][kk, kq] of row j
+#pragma unroll
+    for (int i = 0; i < T; ++i) {
+      R[j][i] = i == j ? 1.f : (i < j ? R[j - 1 > i ? j - 1 : i][i] * dec[j] : 0.f);
+      N[j][i] = i == j ? 1.f : 0.f;
+    }
+    // row j of (I + diag(beta) L)^-1:  N_j = e_j - beta_j sum_{i<j} L_ji N_i
+#pragma unroll
+    for (int i = 0; i < j; ++i) {
+      const float l = j < nv ? beta[j] * R[j][i] * gj[i * 2] : 0.f;
+#pragma unroll
+      for (int c = 0; c <= i; ++c) N[j][c] = fmaf(-l, N[i][c], N[j][c]);
+    }
+    if (j < nv) {
+      float* dst = mats + ((int64_t) (row0 + t0 + j) * a.H + h) * kMatRow;
+#pragma unroll
+      for (int i = 0; i < T; ++i) {
+        dst[i] = i <= j ? N[j][i] * beta[i] : 0.f;
+        dst[T + i] = i <= j ? R[j][i] * gj[i * 2 + 1] : 0.f;
+      }
+      dst[2 * T] = D[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < T; ++j) {
+    if (j < nv) {
+      // D_last / D_j as the product of the decays behind j
+      float f = 1.f;
+#pragma unroll
+      for (int m = 0; m < T; ++m) f *= (m > j && m < nv) ? dec[m] : 1.f;
+      mats[((int64_t) (row0 + t0 + j) * a.H + h) * kMatRow + 2 * T + 1] = f;
+    }
+  }
+}
+
 // One CTA = NW warps = NW * (32 / LPC) value columns of one (sequence, head).  A thread holds DPL state elements of its column:
 // element i is dim index ((i / VEC) * LPC + sub) * VEC + i % VEC (VEC = 4 when DPL allows 16-byte shared loads), so that the
 // lanes of a column read neighbouring pieces of a staged key row.  Staged rows are LDK = LPC * DPL >= dim floats wide, zero behind dim.
-// Shared memory per stage: k [16][LDK] | q [16][LDK] | products [16][8][2] | v [16][COLS] | beta [16] | g [16].
+// Shared memory per stage: k [16][LDK] | q [16][LDK] | block matrices [16][20] | v [16][COLS].
 template <int LPC, int DPL, int NW>
-__global__ void __launch_bounds__(NW * 32) delta_scan_blocked_kernel(float* out, ScanArgs a, const float* gram, int vec4) {
+__global__ void __launch_bounds__(NW * 32) delta_scan_blocked_kernel(float* out, ScanArgs a, const float* mats, int vec4) {
   constexpr int T = kBlk, TCH = kBlkChunk, CPW = 32 / LPC, COLS = NW * CPW, LDK = LPC * DPL, VEC = DPL % 4 == 0 ? 4 : 1, NT = NW * 32;
-  constexpr int STAGE = 2 * TCH * LDK + TCH * T * 2 + TCH * COLS + 2 * TCH;
+  constexpr int MR = kMatRow, STAGE = 2 * TCH * LDK + TCH * MR + TCH * COLS;
   extern __shared__ __align__(16) float smem[];
   const int e = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * COLS;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, sub = lane % LPC;
@@ -275,9 +336,8 @@ __global__ void __launch_bounds__(NW * 32) delta_scan_blocked_kernel(float* out,
   auto stage_in = [&](int c, int buf) {
     float* ks = smem + buf * STAGE;
     float* qs = ks + TCH * LDK;
-    float* gr = qs + TCH * LDK;
-    float* vs = gr + TCH * T * 2;
-    float* bs = vs + TCH * COLS;
+    float* mw = qs + TCH * LDK;
+    float* vs = mw + TCH * MR;
     const int t0 = c * TCH, nt = min(TCH, len - t0);
     const float* ub = a.u + (int64_t) (row0 + t0) * C;
     if (vec4) {
@@ -301,15 +361,10 @@ __global__ void __launch_bounds__(NW * 32) delta_scan_blocked_kernel(float* out,
       const bool ok = t < nt && c_ < a.vdim;
       cp_async_f(vs + i, ok ? ub + (int64_t) t * C + 2 * a.G * a.dim + h * a.vdim + c_ : a.u, ok);
     }
-    for (int i = threadIdx.x; i < TCH * (T * 2 / 4); i += NT) {              // a row's products: 16 floats, 16-byte aligned
-      const int t = i / (T * 2 / 4), p4 = (i % (T * 2 / 4)) * 4;
+    for (int i = threadIdx.x; i < TCH * (MR / 4); i += NT) {                 // a row's block matrices: 20 floats, 16-byte aligned
+      const int t = i / (MR / 4), p4 = (i % (MR / 4)) * 4;
       const bool ok = t < nt;
-      cp_async_f4(gr + t * T * 2 + p4, ok ? gram + ((int64_t) (row0 + t0 + t) * a.G + jh) * T * 2 + p4 : gram, ok);
-    }
-    for (int i = threadIdx.x; i < 2 * TCH; i += NT) {
-      const int t = i % TCH, which = i / TCH;                                // beta, then g
-      const bool ok = t < nt;
-      cp_async_f(bs + i, ok ? a.bg + (int64_t) (row0 + t0 + t) * 2 * a.H + which * a.H + h : a.bg, ok);
+      cp_async_f4(mw + t * MR + p4, ok ? mats + ((int64_t) (row0 + t0 + t) * a.H + h) * MR + p4 : mats, ok);
     }
     cp_async_commit_wait_all(true);
   };
@@ -322,10 +377,8 @@ __global__ void __launch_bounds__(NW * 32) delta_scan_blocked_kernel(float* out,
     if (c + 1 < nch) stage_in(c + 1, (c + 1) & 1);
     const float* ks = smem + (c & 1) * STAGE;
     const float* qs = ks + TCH * LDK;
-    const float* gr = qs + TCH * LDK;
-    const float* vs = gr + TCH * T * 2;
-    const float* bs = vs + TCH * COLS;
-    const float* gs = bs + TCH;
+    const float* mws = qs + TCH * LDK;
+    const float* vs = mws + TCH * MR;
     const int t0 = c * TCH;
 #pragma unroll 1
     for (int b = 0; b < TCH / T; ++b) {
@@ -333,27 +386,32 @@ __global__ void __launch_bounds__(NW * 32) delta_scan_blocked_kernel(float* out,
       if (tb >= len) break;
       const float* kb = ks + b * T * LDK;
       const float* qb = qs + b * T * LDK;
+      // sixteen independent sums advance together: the tokens are the inner loop
       float A[T], B[T];
 #pragma unroll
-      for (int j = 0; j < T; ++j) {
-        float pa = 0.f, pb = 0.f;
-        if constexpr (VEC == 4) {
+      for (int j = 0; j < T; ++j) A[j] = B[j] = 0.f;
+      if constexpr (VEC == 4) {
 #pragma unroll
-          for (int v4 = 0; v4 < DPL / 4; ++v4) {
+        for (int v4 = 0; v4 < DPL / 4; ++v4) {
+#pragma unroll
+          for (int j = 0; j < T; ++j) {
             const float4 kv = *reinterpret_cast<const float4*>(kb + j * LDK + (v4 * LPC + sub) * 4);
             const float4 qv = *reinterpret_cast<const float4*>(qb + j * LDK + (v4 * LPC + sub) * 4);
-            pa = fmaf(S[4 * v4], kv.x, pa); pa = fmaf(S[4 * v4 + 1], kv.y, pa); pa = fmaf(S[4 * v4 + 2], kv.z, pa); pa = fmaf(S[4 * v4 + 3], kv.w, pa);
-            pb = fmaf(S[4 * v4], qv.x, pb); pb = fmaf(S[4 * v4 + 1], qv.y, pb); pb = fmaf(S[4 * v4 + 2], qv.z, pb); pb = fmaf(S[4 * v4 + 3], qv.w, pb);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < DPL; ++i) {
-            pa = fmaf(S[i], kb[j * LDK + dmap(i)], pa);
-            pb = fmaf(S[i], qb[j * LDK + dmap(i)], pb);
+            A[j] = fmaf(S[4 * v4], kv.x, A[j]); B[j] = fmaf(S[4 * v4], qv.x, B[j]);
+            A[j] = fmaf(S[4 * v4 + 1], kv.y, A[j]); B[j] = fmaf(S[4 * v4 + 1], qv.y, B[j]);
+            A[j] = fmaf(S[4 * v4 + 2], kv.z, A[j]); B[j] = fmaf(S[4 * v4 + 2], qv.z, B[j]);
+            A[j] = fmaf(S[4 * v4 + 3], kv.w, A[j]); B[j] = fmaf(S[4 * v4 + 3], qv.w, B[j]);
           }
         }
-        A[j] = pa;
-        B[j] = pb;
+      } else {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+#pragma unroll
+          for (int j = 0; j < T; ++j) {
+            A[j] = fmaf(S[i], kb[j * LDK + dmap(i)], A[j]);
+            B[j] = fmaf(S[i], qb[j * LDK + dmap(i)], B[j]);
+          }
+        }
       }
 #pragma unroll
       for (int o = LPC / 2; o > 0; o >>= 1) {
@@ -363,26 +421,38 @@ __global__ void __launch_bounds__(NW * 32) delta_scan_blocked_kernel(float* out,
           B[j] += __shfl_xor_sync(0xffffffffu, B[j], o);
         }
       }
-      // the dependent part, per column: ut[i] = u_i * (D_j / D_i) as j advances
-      const float* pr = gr + b * T * T * 2;                                 // [j][i][kk, kq]
-      float ut[T], D = 1.f;
+      // per column: r = v - D (S^T k), u = M r, o = D (S^T q) + W u, and the updates' weights u_j D_last / D_j.  Rows behind the
+      // portion's end were staged as zeros: they give u = 0 and are not stored.
+      const float* mw = mws + b * T * MR;
+      const int nv = min(T, len - tb);
+      float r[T], ut[T];
+      float2 df[T];
 #pragma unroll
       for (int j = 0; j < T; ++j) {
-        const bool in = tb + j < len;
-        const float g = in ? gs[b * T + j] : 1.f;                            // a token behind the portion's end changes nothing
-        D *= g;
-        float aj = D * A[j], oj = D * B[j];
-#pragma unroll
-        for (int i = 0; i < j; ++i) {
-          ut[i] *= g;
-          aj = fmaf(pr[(j * T + i) * 2], ut[i], aj);
-          oj = fmaf(pr[(j * T + i) * 2 + 1], ut[i], oj);
-        }
-        const float uj = in ? bs[b * T + j] * (vs[(b * T + j) * COLS + cc] - aj) : 0.f;
-        ut[j] = uj;
-        oj = fmaf(pr[(j * T + j) * 2 + 1], uj, oj);
-        if (in && live && sub == 0) out[((int64_t) (row0 + tb + j) * a.H + h) * a.vdim + col] = oj;
+        df[j] = *reinterpret_cast<const float2*>(mw + j * MR + 2 * T);        // D_j, D_last / D_j
+        r[j] = fmaf(-df[j].x, A[j], vs[(b * T + j) * COLS + cc]);
       }
+#pragma unroll
+      for (int j = 0; j < T; ++j) {
+        const float4 m0 = *reinterpret_cast<const float4*>(mw + j * MR), m1 = *reinterpret_cast<const float4*>(mw + j * MR + 4);
+        const float m[T] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        float uj = 0.f;
+#pragma unroll
+        for (int i = 0; i <= j; ++i) uj = fmaf(m[i], r[i], uj);
+        ut[j] = uj;
+      }
+#pragma unroll
+      for (int j = 0; j < T; ++j) {
+        const float4 w0 = *reinterpret_cast<const float4*>(mw + j * MR + T), w1 = *reinterpret_cast<const float4*>(mw + j * MR + T + 4);
+        const float w[T] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        float oj = df[j].x * B[j];
+#pragma unroll
+        for (int i = 0; i <= j; ++i) oj = fmaf(w[i], ut[i], oj);
+        if (j < nv && live && sub == 0) out[((int64_t) (row0 + tb + j) * a.H + h) * a.vdim + col] = oj;
+      }
+      const float D = mw[(nv - 1) * MR + 2 * T];                              // all of the block's decays
+#pragma unroll
+      for (int j = 0; j < T; ++j) ut[j] *= df[j].y;
       if constexpr (VEC == 4) {
 #pragma unroll
         for (int v4 = 0; v4 < DPL / 4; ++v4) {
@@ -414,21 +484,222 @@ __global__ void __launch_bounds__(NW * 32) delta_scan_blocked_kernel(float* out,
   }
 }
 
+// The form for steps with columns enough to fill the chip: a warp carries FOUR value columns, every lane holding DPL elements of
+// each (a column's `dim` elements spread over all 32 lanes), so a staged key or query element is read from shared memory once per
+// warp and used for four columns.  The 64 partial sums of a block (4 columns x 8 rows x {S^T k, S^T q}) are folded over the lanes
+// — each stage halves the values a lane keeps — so that after five stages lane 8 c + j holds the two sums of column c, row j;
+// u = M r and o = D (S^T q) + W u then run across the eight lanes of a column with shuffles, and the weights of the rank-one updates
+// are handed back to all lanes.
+template <int DPL>
+__global__ void __launch_bounds__(128) delta_scan_tiled_kernel(float* out, ScanArgs a, const float* mats, int vec4) {
+  constexpr int T = kBlk, TCH = kBlkChunk, CT = 4, NW = 4, COLS = NW * CT, LDK = 32 * DPL, VEC = DPL % 4 == 0 ? 4 : 1, NT = NW * 32;
+  constexpr int MR = kMatRow, STAGE = 2 * TCH * LDK + TCH * MR + TCH * COLS;
+  extern __shared__ __align__(16) float smem[];
+  const int e = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * COLS;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int len = a.seq_len[e], past = a.seq_past[e], row0 = a.seq_start[e];
+  const int jh = h / (a.H / a.G);
+  const int C = 2 * a.G * a.dim + a.H * a.vdim;
+  auto dmap = [&](int i) { return ((i / VEC) * 32 + lane) * VEC + i % VEC; };
+  float* sp = a.state + ((int64_t) a.seq_slot[e] * a.H + h) * a.vdim * a.dim;
+  float S[CT][DPL];
+#pragma unroll
+  for (int c = 0; c < CT; ++c) {
+    const int col = c0 + warp * CT + c;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      const int d = dmap(i);
+      S[c][i] = (col < a.vdim && past > 0 && d < a.dim) ? sp[(int64_t) col * a.dim + d] : 0.f;
+    }
+  }
+  for (int i = threadIdx.x; i < 2 * STAGE; i += NT) smem[i] = 0.f;
+  __syncthreads();
+  auto stage_in = [&](int c, int buf) {
+    float* ks = smem + buf * STAGE;
+    float* qs = ks + TCH * LDK;
+    float* mw = qs + TCH * LDK;
+    float* vs = mw + TCH * MR;
+    const int t0 = c * TCH, nt = min(TCH, len - t0);
+    const float* ub = a.u + (int64_t) (row0 + t0) * C;
+    if (vec4) {
+      const int per = a.dim / 4;
+      for (int i = threadIdx.x; i < TCH * per; i += NT) {
+        const int t = i / per, d = (i % per) * 4;
+        const bool ok = t < nt;
+        cp_async_f4(qs + t * LDK + d, ok ? ub + (int64_t) t * C + jh * a.dim + d : a.u, ok);
+        cp_async_f4(ks + t * LDK + d, ok ? ub + (int64_t) t * C + (a.G + jh) * a.dim + d : a.u, ok);
+      }
+    } else {
+      for (int i = threadIdx.x; i < TCH * a.dim; i += NT) {
+        const int t = i / a.dim, d = i % a.dim;
+        const bool ok = t < nt;
+        cp_async_f(qs + t * LDK + d, ok ? ub + (int64_t) t * C + jh * a.dim + d : a.u, ok);
+        cp_async_f(ks + t * LDK + d, ok ? ub + (int64_t) t * C + (a.G + jh) * a.dim + d : a.u, ok);
+      }
+    }
+    for (int i = threadIdx.x; i < TCH * COLS; i += NT) {
+      const int t = i / COLS, c_ = c0 + i % COLS;
+      const bool ok = t < nt && c_ < a.vdim;
+      cp_async_f(vs + i, ok ? ub + (int64_t) t * C + 2 * a.G * a.dim + h * a.vdim + c_ : a.u, ok);
+    }
+    for (int i = threadIdx.x; i < TCH * (MR / 4); i += NT) {
+      const int t = i / (MR / 4), p4 = (i % (MR / 4)) * 4;
+      const bool ok = t < nt;
+      cp_async_f4(mw + t * MR + p4, ok ? mats + ((int64_t) (row0 + t0 + t) * a.H + h) * MR + p4 : mats, ok);
+    }
+    cp_async_commit_wait_all(true);
+  };
+  const int nch = (len + TCH - 1) / TCH;
+  if (nch > 0) stage_in(0, 0);
+  const int cl = lane >> 3, jl = lane & 7;                                   // after the fold this lane owns (column cl, row jl)
+  for (int c = 0; c < nch; ++c) {
+    cp_async_commit_wait_all(false);
+    __syncthreads();
+    if (c + 1 < nch) stage_in(c + 1, (c + 1) & 1);
+    const float* ks = smem + (c & 1) * STAGE;
+    const float* qs = ks + TCH * LDK;
+    const float* mws = qs + TCH * LDK;
+    const float* vs = mws + TCH * MR;
+    const int t0 = c * TCH;
+#pragma unroll 1
+    for (int b = 0; b < TCH / T; ++b) {
+      const int tb = t0 + b * T;
+      if (tb >= len) break;
+      const float* kb = ks + b * T * LDK;
+      const float* qb = qs + b * T * LDK;
+      float x[CT * T * 2];                                                   // index (c * 8 + j) * 2 + {S^T k, S^T q}
+#pragma unroll
+      for (int v = 0; v < CT * T * 2; ++v) x[v] = 0.f;
+#pragma unroll
+      for (int i0 = 0; i0 < DPL; i0 += VEC) {
+#pragma unroll
+        for (int j = 0; j < T; ++j) {
+          float kv[VEC], qv[VEC];
+          if constexpr (VEC == 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kb + j * LDK + ((i0 / 4) * 32 + lane) * 4);
+            const float4 q4 = *reinterpret_cast<const float4*>(qb + j * LDK + ((i0 / 4) * 32 + lane) * 4);
+            kv[0] = k4.x; kv[1] = k4.y; kv[2] = k4.z; kv[3] = k4.w;
+            qv[0] = q4.x; qv[1] = q4.y; qv[2] = q4.z; qv[3] = q4.w;
+          } else {
+            kv[0] = kb[j * LDK + dmap(i0)];
+            qv[0] = qb[j * LDK + dmap(i0)];
+          }
+#pragma unroll
+          for (int cc = 0; cc < CT; ++cc)
+#pragma unroll
+            for (int w = 0; w < VEC; ++w) {
+              x[(cc * T + j) * 2] = fmaf(S[cc][i0 + w], kv[w], x[(cc * T + j) * 2]);
+              x[(cc * T + j) * 2 + 1] = fmaf(S[cc][i0 + w], qv[w], x[(cc * T + j) * 2 + 1]);
+            }
+        }
+      }
+      // fold: a lane whose bit is set keeps the upper half of its values, hands the lower half over, and adds what it receives
+#pragma unroll
+      for (int st = 0; st < 5; ++st) {
+        const int o = 16 >> st, half = (CT * T * 2) >> (st + 1);
+        const bool up = lane & o;
+#pragma unroll
+        for (int m = 0; m < half; ++m) {
+          const float send = up ? x[m] : x[m + half];
+          const float keep = up ? x[m + half] : x[m];
+          x[m] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+        }
+      }
+      const float* mw = mws + b * T * MR;
+      const int nv = min(T, len - tb);
+      const float2 df = *reinterpret_cast<const float2*>(mw + jl * MR + 2 * T);        // D_j, D_last / D_j of this lane's row
+      const float r = fmaf(-df.x, x[0], vs[(b * T + jl) * COLS + warp * CT + cl]);
+      const float4 m0 = *reinterpret_cast<const float4*>(mw + jl * MR), m1 = *reinterpret_cast<const float4*>(mw + jl * MR + 4);
+      const float4 w0 = *reinterpret_cast<const float4*>(mw + jl * MR + T), w1 = *reinterpret_cast<const float4*>(mw + jl * MR + T + 4);
+      const float mr[T] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+      const float wr[T] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      float uj = 0.f;
+#pragma unroll
+      for (int i = 0; i < T; ++i) uj = fmaf(mr[i], __shfl_sync(0xffffffffu, r, (lane & 24) | i), uj);      // entries behind the row are zero
+      float oj = df.x * x[1];
+#pragma unroll
+      for (int i = 0; i < T; ++i) oj = fmaf(wr[i], __shfl_sync(0xffffffffu, uj, (lane & 24) | i), oj);
+      const int col = c0 + warp * CT + cl;
+      if (jl < nv && col < a.vdim) out[((int64_t) (row0 + tb + jl) * a.H + h) * a.vdim + col] = oj;
+      const float ut = uj * df.y;
+      const float D = mw[(nv - 1) * MR + 2 * T];
+#pragma unroll
+      for (int cc = 0; cc < CT; ++cc)
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) S[cc][i] *= D;
+#pragma unroll
+      for (int j = 0; j < T; ++j) {
+        float uc[CT];
+#pragma unroll
+        for (int cc = 0; cc < CT; ++cc) uc[cc] = __shfl_sync(0xffffffffu, ut, cc * 8 + j);
+#pragma unroll
+        for (int i0 = 0; i0 < DPL; i0 += VEC) {
+          float kv[VEC];
+          if constexpr (VEC == 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kb + j * LDK + ((i0 / 4) * 32 + lane) * 4);
+            kv[0] = k4.x; kv[1] = k4.y; kv[2] = k4.z; kv[3] = k4.w;
+          } else {
+            kv[0] = kb[j * LDK + dmap(i0)];
+          }
+#pragma unroll
+          for (int cc = 0; cc < CT; ++cc)
+#pragma unroll
+            for (int w = 0; w < VEC; ++w) S[cc][i0 + w] = fmaf(uc[cc], kv[w], S[cc][i0 + w]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < CT; ++c) {
+    const int col = c0 + warp * CT + c;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      const int d = dmap(i);
+      if (col < a.vdim && d < a.dim) sp[(int64_t) col * a.dim + d] = S[c][i];
+    }
+  }
+}
+
+template <int DPL>
+int launch_scan_tiled(float* out, const ScanArgs& a, const float* mats, int seqs, cudaStream_t s) {
+  constexpr int COLS = 16, LDK = 32 * DPL;
+  constexpr size_t smem = (size_t) 2 * (2 * kBlkChunk * LDK + kBlkChunk * kMatRow + kBlkChunk * COLS) * sizeof(float);
+  static bool raised = false;
+  if (!raised && smem > 48 * 1024) {
+    TB_CHECK_CUDA(cudaFuncSetAttribute(delta_scan_tiled_kernel<DPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    raised = true;
+  }
+  const int C = 2 * a.G * a.dim + a.H * a.vdim;
+  const int vec4 = a.dim % 4 == 0 && C % 4 == 0 && (uintptr_t) a.u % 16 == 0;
+  dim3 grid((a.vdim + COLS - 1) / COLS, a.H, seqs);
+  delta_scan_tiled_kernel<DPL><<<grid, 128, smem, s>>>(out, a, mats, vec4);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// the blocks' products and inverted systems (workspace: gram [rows][G][16], then mats [rows][H][20]) -> mats
+const float* prepare_blocks(const ScanArgs& a, float* workspace, int rows, int seqs, int max_len, cudaStream_t s) {
+  const int nblk = (max_len + kBlk - 1) / kBlk;
+  float* mats = workspace + (int64_t) rows * a.G * kBlk * 2;
+  delta_gram_kernel<<<dim3(nblk, a.G, seqs), 256, 0, s>>>(workspace, a);
+  const int64_t items = (int64_t) seqs * a.H * nblk;
+  delta_block_matrices_kernel<<<(unsigned) ((items + 127) / 128), 128, 0, s>>>(mats, workspace, a, nblk, seqs);
+  return mats;
+}
+
 template <int LPC, int DPL, int NW>
-int launch_scan_blocked(float* out, const ScanArgs& a, float* gram, int seqs, int max_len, cudaStream_t s) {
+int launch_scan_blocked(float* out, const ScanArgs& a, const float* mats, int seqs, cudaStream_t s) {
   constexpr int COLS = NW * (32 / LPC), LDK = LPC * DPL;
-  constexpr size_t smem = (size_t) 2 * (2 * kBlkChunk * LDK + kBlkChunk * kBlk * 2 + kBlkChunk * COLS + 2 * kBlkChunk) * sizeof(float);
+  constexpr size_t smem = (size_t) 2 * (2 * kBlkChunk * LDK + kBlkChunk * kMatRow + kBlkChunk * COLS) * sizeof(float);
   static bool raised = false;
   if (!raised && smem > 48 * 1024) {
     TB_CHECK_CUDA(cudaFuncSetAttribute(delta_scan_blocked_kernel<LPC, DPL, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     raised = true;
   }
-  delta_gram_kernel<<<dim3((max_len + kBlk - 1) / kBlk, a.G, seqs), 256, 0, s>>>(gram, a);
-  TB_CHECK_CUDA(cudaGetLastError());
   const int C = 2 * a.G * a.dim + a.H * a.vdim;
   const int vec4 = a.dim % 4 == 0 && C % 4 == 0 && LDK % 4 == 0 && (uintptr_t) a.u % 16 == 0;
   dim3 grid((a.vdim + COLS - 1) / COLS, a.H, seqs);
-  delta_scan_blocked_kernel<LPC, DPL, NW><<<grid, NW * 32, smem, s>>>(out, a, gram, vec4);
+  delta_scan_blocked_kernel<LPC, DPL, NW><<<grid, NW * 32, smem, s>>>(out, a, mats, vec4);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -471,6 +742,8 @@ int launch_scan(float* out, const ScanArgs& a, int seqs, cudaStream_t s) {
 
 using namespace tb;
 static inline bool dt_ok(int d) { return d == TB_DT_F32 || d == TB_DT_BF16; }
+static int g_scan_mode = 0;
+extern "C" int tb_delta_scan_set_mode(int mode) { g_scan_mode = mode; return 0; }
 
 extern "C" int tb_delta_prepare(float* u, float* bg, const float* proj, int64_t ldp, const void* conv_w, const void* a_log,
                                 const void* dt_bias, int w_dtype, int col_b, int col_a, const float* state, float* state_rw,
@@ -492,8 +765,8 @@ extern "C" int tb_delta_prepare(float* u, float* bg, const float* proj, int64_t 
 }
 
 extern "C" int tb_delta_rule_scan(float* out, const float* u, const float* bg, float* state, const int* seq_start, const int* seq_len,
-                                  const int* seq_past, const int* seq_slot, int seqs, int heads, int kv_heads, int dim, int vdim,
-                                  int max_len, float* workspace, tb_stream_t stream) {
+                                  const int* seq_past, const int* seq_slot, int rows, int seqs, int heads, int kv_heads, int dim,
+                                  int vdim, int max_len, float* workspace, tb_stream_t stream) {
   if (!out || !u || !bg || !state || !seq_start || !seq_len || !seq_past || !seq_slot) return -1;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || dim > 512 || vdim <= 0 || seqs < 0 || seqs > 65535 || heads > 65535)
     return -1;
@@ -501,19 +774,21 @@ extern "C" int tb_delta_rule_scan(float* out, const float* u, const float* bg, f
   ScanArgs a{u, bg, state, seq_start, seq_len, seq_past, seq_slot, heads, kv_heads, dim, vdim};
   cudaStream_t s = (cudaStream_t) stream;
   if (max_len >= 3 && workspace) {
-    // prompt portions: eight tokens at a time; a column on 8 lanes when that still gives the chip warps enough
-    const bool narrow = (int64_t) seqs * heads * vdim >= 1200 && dim <= 128;
-    const int ldk = dim <= 32 ? 32 : dim <= 64 ? 64 : dim <= 128 ? 128 : dim <= 256 ? 256 : 512;
-    if (narrow) {
-      if (ldk == 32) return launch_scan_blocked<8, 4, 4>(out, a, workspace, seqs, max_len, s);
-      if (ldk == 64) return launch_scan_blocked<8, 8, 4>(out, a, workspace, seqs, max_len, s);
-      return launch_scan_blocked<8, 16, 4>(out, a, workspace, seqs, max_len, s);
+    // prompt portions: eight rows at a time; four columns per warp when there are columns enough to fill the chip that way
+    const float* mats = prepare_blocks(a, workspace, rows, seqs, max_len, s);
+    TB_CHECK_CUDA(cudaGetLastError());
+    const bool tiled = dim <= 256 && (g_scan_mode == 1 || (g_scan_mode == 0 && (int64_t) seqs * heads * vdim >= 1200));
+    if (tiled) {
+      if (dim <= 32) return launch_scan_tiled<1>(out, a, mats, seqs, s);
+      if (dim <= 64) return launch_scan_tiled<2>(out, a, mats, seqs, s);
+      if (dim <= 128) return launch_scan_tiled<4>(out, a, mats, seqs, s);
+      return launch_scan_tiled<8>(out, a, mats, seqs, s);
     }
-    if (ldk == 32) return launch_scan_blocked<32, 1, 8>(out, a, workspace, seqs, max_len, s);
-    if (ldk == 64) return launch_scan_blocked<32, 2, 8>(out, a, workspace, seqs, max_len, s);
-    if (ldk == 128) return launch_scan_blocked<32, 4, 8>(out, a, workspace, seqs, max_len, s);
-    if (ldk == 256) return launch_scan_blocked<32, 8, 8>(out, a, workspace, seqs, max_len, s);
-    return launch_scan_blocked<32, 16, 8>(out, a, workspace, seqs, max_len, s);
+    if (dim <= 32) return launch_scan_blocked<32, 1, 8>(out, a, mats, seqs, s);
+    if (dim <= 64) return launch_scan_blocked<32, 2, 8>(out, a, mats, seqs, s);
+    if (dim <= 128) return launch_scan_blocked<32, 4, 8>(out, a, mats, seqs, s);
+    if (dim <= 256) return launch_scan_blocked<32, 8, 8>(out, a, mats, seqs, s);
+    return launch_scan_blocked<32, 16, 8>(out, a, mats, seqs, s);
   }
   const int dpl = (dim + 31) / 32;
   if (dpl <= 1) return launch_scan<1>(out, a, seqs, s);

@@ -682,9 +682,10 @@ def delta_rule_scan(u, bg, state, batch, heads, kv_heads, dim, vdim):
     out = torch.empty((u.shape[0], heads, vdim), dtype=torch.float32, device=u.device)
     ws = None
     if batch.max_len >= 3 and not FORCE_SERIAL_SCAN:      # prompt portions: eight rows at a time over the blocks' own k.k and k.q products
-        ws = torch.empty((u.shape[0], kv_heads, 16), dtype=torch.float32, device=u.device)
+        ws = torch.empty((u.shape[0] * (16 * kv_heads + 20 * heads),), dtype=torch.float32, device=u.device)
     check(_rl.tb_delta_rule_scan(_p(out), _p(u), _p(bg), _p(state), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
-                                 _p(batch.seq_slot), batch.num_seqs, heads, kv_heads, dim, vdim, batch.max_len, _p(ws), _stream()),
+                                 _p(batch.seq_slot), u.shape[0], batch.num_seqs, heads, kv_heads, dim, vdim, batch.max_len, _p(ws),
+                                 _stream()),
           "tb_delta_rule_scan")
     return out
 
