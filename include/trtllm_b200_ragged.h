@@ -248,6 +248,9 @@ int tb_delta_prepare(float* u, float* bg, const float* proj, int64_t ldp, const 
 int tb_delta_rule_scan(float* out, const float* u, const float* bg, float* state, const int* seq_start, const int* seq_len,
                        const int* seq_past, const int* seq_slot, int rows, int seqs, int heads, int kv_heads, int dim, int vdim,
                        int max_len, float* workspace, tb_stream_t stream);
+/* A/B switch for measurements: which prompt kernel tb_delta_rule_scan takes.  0: by the number of value columns (default);
+ * 1: four columns per warp whenever dim <= 256; 3: one column per warp. */
+int tb_delta_scan_set_mode(int mode);
 /* out T [N, heads, vdim] = o / sqrt(mean_vdim(o^2) + eps) * w * silu(gate): o fp32 [N, heads, vdim]; w [vdim] shared by the heads
  * (NULL: none); gate fp32 logits [N, >= heads * vdim] with row stride ldg (NULL: none). */
 int tb_gated_rmsnorm_heads(void* out, int dtype, const float* o, const float* gate, int64_t ldg, const void* w, int w_dtype, float eps,

@@ -225,6 +225,7 @@ RAGGED_SIGNATURES = {
     "tb_delta_prepare": (i32, [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
                                i32, f32, vp]),
     "tb_delta_rule_scan": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp]),
+    "tb_delta_scan_set_mode": (i32, [i32]),
     "tb_gated_rmsnorm_heads": (i32, [vp, i32, vp, vp, i64, vp, i32, f32, i32, i32, i32, vp]),
 }
 SIGNATURES.update(RAGGED_SIGNATURES)

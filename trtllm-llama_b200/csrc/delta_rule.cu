@@ -6,7 +6,8 @@
 //   delta_prepare_kernel   one CTA per row over the stacked projection q | k | v | (further columns): short causal convolution over
 //                          the row's portion and the sequence's carried inputs, SiLU, then per head x / sqrt(sum x^2 + eps_unit)
 //                          for queries (times dim^-1/2) and keys; beta = sigmoid(b) and g = exp(-exp(A_log) softplus(a + dt_bias))
-//                          per head.  A sequence that brings ONE row has its carried inputs moved on here.
+//                          per head.  A sequence that brings ONE row has its carried inputs moved on here.  Steps of few rows
+//                          spread a row's channels over several CTAs.
 //   delta_scan_kernel      the columns of S are independent recurrences: one warp per (sequence, head, value column), the lanes
 //                          hold the column's `dim` state elements (dim / 32 each).  Per token two dot products are reduced over
 //                          the lanes at once, a = S^T k and b = S^T q of the OLD state, and with k . q (computed when the
@@ -33,6 +34,8 @@
 //   delta_gram_kernel      KK and KQ of every block of eight rows of a portion (blocks count from the portion's first row).
 //   gated_rmsnorm_heads    one warp per (row, head): o / sqrt(mean(o^2) + eps) * w * silu(gate), stored in the storage type.
 #include <cuda_bf16.h>
+
+#include <algorithm>
 
 #include "common.cuh"
 #include "../../include/trtllm_b200_ragged.h"
@@ -92,7 +95,7 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(float* u, float* bg,
     st_rw[(int64_t) (n - 1) * C + c] = a.proj[(int64_t) row * a.ldp + c];
   };
   // queries and keys: a warp per head vector
-  for (int v = warp; v < 2 * a.G; v += 8) {
+  for (int v = blockIdx.y * 8 + warp; v < 2 * a.G; v += 8 * gridDim.y) {
     const int c0 = v * a.dim;
     float ss = 0.f;
     for (int d = lane; d < a.dim; d += 32) {
@@ -105,11 +108,11 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(float* u, float* bg,
     if (v < a.G) f *= 1.f / sqrtf((float) a.dim);
     for (int d = lane; d < a.dim; d += 32) ur[c0 + d] *= f;       // a lane re-reads what it wrote itself
   }
-  for (int c = Cqk + threadIdx.x; c < C; c += 256) {
+  for (int c = Cqk + blockIdx.y * 256 + threadIdx.x; c < C; c += 256 * gridDim.y) {
     ur[c] = conv_silu_at(a, st, C, c, pos, past, start);
     if (carry) move_on(c);
   }
-  for (int h = threadIdx.x; h < a.H; h += 256) {
+  for (int h = threadIdx.x; h < a.H && blockIdx.y == 0; h += 256) {
     const float* pr = a.proj + (int64_t) row * a.ldp;
     bg[(int64_t) row * 2 * a.H + h] = 1.f / (1.f + expf(-pr[a.col_b + h]));
     const float rate = expf(ld_w(a.a_log, a.w_dtype, h)) * softplus_f(pr[a.col_a + h] + ld_w(a.dt_bias, a.w_dtype, h));
@@ -759,7 +762,10 @@ extern "C" int tb_delta_prepare(float* u, float* bg, const float* proj, int64_t 
   if (rows == 0) return 0;
   PrepArgs a{proj, ldp, conv_w, w_dtype, state, state_rw, a_log, dt_bias, col_b, col_a, tok_seq, tok_pos, seq_start, seq_len,
              seq_past, seq_slot, heads, kv_heads, dim, vdim, taps, eps_unit};
-  delta_prepare_kernel<<<rows, 256, 0, (cudaStream_t) stream>>>(u, bg, a);
+  // one CTA per row when the rows alone fill the chip; a step of few rows also spreads a row's channels over CTAs
+  const int C = 2 * kv_heads * dim + heads * vdim;
+  const int ysplit = rows >= 296 ? 1 : std::max(1, std::min((C + 511) / 512, (296 + rows - 1) / rows));
+  delta_prepare_kernel<<<dim3(rows, ysplit), 256, 0, (cudaStream_t) stream>>>(u, bg, a);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
