@@ -30,7 +30,7 @@ def _close(got, want, dtype, what, scale=1.0):
 AT_ODD = dict(type="attention", heads=6, kv_heads=2, dim=10, vdim=6, diff=0.3, q_temp=(0.7, 5), scale=0.5)
 AT_MQ = dict(type="attention", heads=5, kv_heads=1, dim=8, vdim=40, diff=0.0, scale=0.6)                     # group of 5 > 4 warps, no temperature
 AT_MH = dict(type="attention", heads=3, kv_heads=3, dim=16, vdim=16, diff=0.6, q_temp=(0.25, 1), scale=0.3)  # a group of one
-AT_TC = dict(type="attention", heads=8, kv_heads=2, dim=32, vdim=32, diff=0.5, q_temp=(0.5, 16), scale=0.25)  # tensor-core sizes
+AT_TC = dict(type="attention", heads=8, kv_heads=2, dim=32, vdim=32, diff=0.45, q_temp=(0.6, 16), scale=0.25)  # tensor-core sizes
 DL_ODD = dict(type="delta", heads=6, kv_heads=2, dim=10, vdim=7, conv=3)
 DL_ONE = dict(type="delta", heads=3, kv_heads=3, dim=48, vdim=9, conv=1)          # no convolution, one query head per head
 DL_BIG = dict(type="delta", heads=4, kv_heads=1, dim=64, vdim=32, conv=4)
@@ -318,13 +318,13 @@ def test_differential_attention_head_sizes(d, dv, H, G):
     g = torch.Generator().manual_seed(d * 7 + dv)
     q, k, v = torch.randn(P, H, 2, d, generator=g).to(dt), torch.randn(P, G, 2, d, generator=g).to(dt), torch.randn(P, G, dv, generator=g).to(dt)
     lam4 = [torch.randn(d, generator=g) * 0.1 for _ in range(4)]
-    want = _diff_attention_plain(q, k, v, [x.to(dt) for x in lam4], d ** -0.5 * 2, 0.3, 1e-6, 0.5, 128)
+    want = _diff_attention_plain(q, k, v, [x.to(dt) for x in lam4], d ** -0.5 * 2, 0.3, 1e-6, 0.4, 100)
     blocks = torch.randperm(-(-P // page), generator=g).tolist()
     outs = {}
     for simt in (False, True):
         ops.FORCE_SIMT_ATTENTION = simt
         try:
-            outs[simt] = _diff_attention_ops(q.float(), k.float(), v.float(), lam4, d ** -0.5 * 2, 0.3, 1e-6, 0.5, 128, [P - 3, 1, 1, 1], dt, page, blocks)
+            outs[simt] = _diff_attention_ops(q.float(), k.float(), v.float(), lam4, d ** -0.5 * 2, 0.3, 1e-6, 0.4, 100, [P - 3, 1, 1, 1], dt, page, blocks)
         finally:
             ops.FORCE_SIMT_ATTENTION = False
     _close(outs[True], want, dt, f"SIMT attention {d}/{dv}")

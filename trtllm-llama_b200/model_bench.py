@@ -121,11 +121,11 @@ def random_mimolix(torch, s, seed=0):
         std = std if std is not None else shape[-1] ** -0.5
         return (torch.randn(*shape, generator=g) * std).to(torch.bfloat16)
 
-    att = dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=d ** -0.5, diff=0.5, q_temp=dict(coef=0.5, every=1024))
+    att = dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=d ** -0.5, diff=0.4, q_temp=dict(coef=0.3, every=1024))
     dlt = dict(heads=DH, kv_heads=DG, dim=dd, vdim=ddv, conv=4)
-    moe = dict(kind="moe", expert=dict(ff=s["eff"]), router=dict(experts=s["experts"], top=s["top"], scale=2.0), shared=dict(ff=s["eff"]))
+    moe = dict(kind="moe", expert=dict(ff=s["eff"]), router=dict(experts=s["experts"], top=s["top"], scale=1.5), shared=dict(ff=s["eff"]))
     layers = [dict(type=ty, mixer=dict(att if ty == "attention" else dlt), mlp=moe) for ty in ("delta", "attention", "delta", "attention")]
-    cfg = dict(architecture="Mimolix", vocab=s["vocab"], width=W, embedding=dict(scale=1.0), norm=dict(eps=1e-6), residual_mult=0.7,
+    cfg = dict(architecture="Mimolix", vocab=s["vocab"], width=W, embedding=dict(scale=1.0), norm=dict(eps=1e-6), residual_mult=0.8,
                loop=dict(start=1, stop=3, times=2), layers=layers)
     t = {"embed": n(s["vocab"], W, std=1.0), "head": n(s["vocab"], W), "final.norm": n(W, std=0.1) + 1, "final.norm.b": n(W, std=0.1),
          "loop.in": n(W, 2 * W)}
