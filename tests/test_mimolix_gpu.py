@@ -332,7 +332,7 @@ def test_differential_attention_head_sizes(d, dv, H, G):
 
 
 @pytest.mark.parametrize("cuts", [[600], [1] * 40 + [560], [17, 16, 15, 2, 250, 300], [599, 1]])
-@pytest.mark.parametrize("H,G,d,dv", [(4, 2, 16, 12), (2, 1, 64, 8), (3, 3, 40, 33), (16, 4, 128, 80), (40, 8, 24, 32)])
+@pytest.mark.parametrize("H,G,d,dv", [(4, 2, 16, 12), (2, 1, 64, 8), (3, 3, 40, 33), (16, 4, 128, 80), (40, 8, 24, 32), (30, 6, 10, 50), (10, 2, 130, 128)])
 def test_delta_rule_remembers_far_tokens(H, G, d, dv, cuts):
     """The recurrence over 600 tokens with decays close to 1, so that what was written hundreds of tokens ago still decides the
     read-out: cut into portions (state carried in a slot that held another sequence's state) against the plain loop."""
