@@ -28,6 +28,11 @@ enum { TB_ACT_NONE = 0, TB_ACT_GELU_TANH = 1, TB_ACT_GATED = 2 /* tb_linear_gate
 /* tb_linear compute paths: AUTO = tensor cores for bf16 weights, FMA for fp32 weights; FMA32 = fp32 multiply-add in a
  * fixed k order whatever the storage type (the all-32-bit mode, and the small products that feed a recurrence). */
 enum { TB_COMPUTE_AUTO = 0, TB_COMPUTE_FMA32 = 1, TB_COMPUTE_TILES = 2 /* bf16: the warp-MMA tiles at any row count (A/B) */ };
+/* gated activations of a feed-forward's (gate, up) pair: SIGMOID = g' * sigmoid(alpha g') * (u' + up_shift) with g' = min(g, limit),
+ * u' = clamp(u, -limit, limit) (limit <= 0: no clamp; alpha 1, shift 0 is silu(g) * u); GELU_TANH = gelu_tanh(g) * u. */
+enum { TB_GATE_SIGMOID = 0, TB_GATE_GELU_TANH = 1 };
+/* which elements of a head a rotation pairs: (2i, 2i + 1), or (i, i + dims / 2) */
+enum { TB_ROPE_INTERLEAVED = 0, TB_ROPE_HALF = 1 };
 
 /* C[b][m, n] = act( sum_k A[b][m, k] * W[b][n, k] + bias[b][n] ),  b < batch.
  * A: a_dtype, row stride lda, batch stride a_bs (elements).  W: w_dtype, [N, K] rows contiguous, batch stride w_bs.
@@ -38,11 +43,11 @@ int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const void* a, in
               int act, int compute, tb_stream_t stream);
 
 /* Gated feed-forward input side in one kernel, for generation steps (<= 8 rows, bf16 weights, 8 | K):
- * out[m, j] = g * sigmoid(alpha * g) * (u + up_shift), g = min(a[m] . w[j], limit), u = clamp(a[m] . w[ff + j], -limit, limit),
+ * out[m, j] = the gated activation `gate` (TB_GATE_*) of g = a[m] . w[j] and u = a[m] . w[ff + j],
  * w [2 ff, K] = gate rows, then up rows.  Returns -3 when the shape is not one the streaming kernel takes; the caller
  * then runs tb_linear + tb_gated_act, which compute the same. */
 int tb_linear_gated(void* c, int c_dtype, int64_t ldc, const void* a, int a_dtype, int64_t lda, const void* w, int w_dtype,
-                    int M, int ff, int K, float alpha, float limit, float up_shift, tb_stream_t stream);
+                    int M, int ff, int K, int gate, float alpha, float limit, float up_shift, tb_stream_t stream);
 
 /* Prompt-sized products of bf16 operands on the 5th-generation tensor cores (tcgen05 / TMEM / TMA, the kernel of
  * tb_gemm_tc with bf16 formats): c = act(x w^T + bias); x [M, K], w [N, K] bf16 contiguous, 8 | K, both 16-byte aligned;
@@ -56,6 +61,11 @@ int tb_cast_rows_bf16(void* out, const float* x, int64_t ld, int rows, int cols,
 /* out[n, :] = table[ids[n], :] * scale  (fp32 residual stream; ids clamped into [0, vocab)). */
 int tb_embed_scaled(float* out, const void* table, int t_dtype, const int* ids, float scale, int rows, int width,
                     int vocab, tb_stream_t stream);
+/* The same plus a hashed embedding of the (previous, current) token pair: out[n, :] += pair[r, :] with
+ * r = (prev_ids[n] * mul_prev + ids[n] * mul_cur) mod buckets, or r = buckets (the last row of pair [buckets + 1, width]) for a
+ * token without a predecessor (prev_ids[n] < 0).  pair has the table's type. */
+int tb_embed_bigram(float* out, const void* table, const void* pair, int t_dtype, const int* ids, const int* prev_ids, float scale,
+                    int rows, int width, int vocab, int buckets, int mul_prev, int mul_cur, tb_stream_t stream);
 
 /* y = out_scale * x / sqrt(mean(x^2) + eps) * (w + w_offset) over `cols` columns of each row; x fp32 with row stride ldi.
  * accumulate != 0: out (fp32) += y — the residual update of a layer that normalises the sublayer's OUTPUT (out_scale is
@@ -84,6 +94,23 @@ int tb_layernorm_rows(void* out, int out_dtype, int64_t ldo, const float* x, int
 int tb_residual_layernorm_rows(float* x, int64_t ldx, const float* y1, int64_t ldy1, const float* y2, int64_t ldy2, float out_scale,
                                const void* w, const void* b, int w_dtype, float eps, void* h, int h_dtype, int64_t ldh, int rows,
                                int cols, tb_stream_t stream);
+/* The residual step of a sublayer that sits between two layer norms, with the next sublayer's input, in one pass:
+ * x <- x + out_scale * LN(y; w_post, b_post), then h = LN(x; w_pre, b_pre) stored as h_dtype (w_pre == NULL: only the residual
+ * step).  Biases may be NULL.  Computes what tb_layernorm_rows, the sum and tb_layernorm_rows compute. */
+int tb_residual_sandwich_layernorm_rows(float* x, int64_t ldx, const float* y, int64_t ldy, const void* w_post, const void* b_post,
+                                        const void* w_pre, const void* b_pre, int w_dtype, float eps, float out_scale, void* h,
+                                        int h_dtype, int64_t ldh, int rows, int cols, tb_stream_t stream);
+/* Per-layer token input, one kernel per layer: e = side_embed[ids[n], e_off : e_off + sd] (row stride lde), g = gelu_tanh(w_gate x)
+ * * e (w_gate [sd, width]), y = w_proj g (w_proj [width, sd]), x <- x + y / sqrt(mean(y^2) + eps) * norm_w.  The operands of the two
+ * products are rounded to the storage type w_dtype; sums, norm and residual are fp32.  With w_pre the next layer's input leaves the
+ * same kernel: h = LN(x; w_pre, b_pre), or x / rms(x) * w_pre when pre_rms != 0. */
+int tb_token_side_input(float* x, int64_t ldx, const void* side_embed, int64_t lde, int e_off, const int* ids, int vocab,
+                        const void* w_gate, const void* w_proj, const void* norm_w, int w_dtype, float eps, int rows, int width, int sd,
+                        const void* w_pre, const void* b_pre, int pre_rms, void* h, int h_dtype, int64_t ldh, tb_stream_t stream);
+/* out fp32 = out_scale * (a / rms(a) * wa + b / rms(b) * wb): two mixers side by side, each RMS-normalised over the row with its
+ * own weight (a, b fp32 rows). */
+int tb_rmsnorm_pair_sum(float* out, int64_t ldo, const float* a, int64_t lda, const float* b, int64_t ldb, const void* wa,
+                        const void* wb, int w_dtype, float eps, float out_scale, int rows, int cols, tb_stream_t stream);
 /* out[r] = [a[r, :cols_a] | b[r, :cols_b]] (fp32 inputs with row strides lda / ldb) in out_dtype, contiguous: the operand of a
  * projection that reads two streams side by side. */
 int tb_concat_rows(void* out, int out_dtype, const float* a, int64_t lda, int cols_a, const float* b, int64_t ldb, int cols_b,
@@ -96,10 +123,11 @@ int tb_add_row_vector(float* x, int64_t ld, const void* vec, int v_dtype, int ro
 /* x <- cap * tanh(x / cap), in place over n fp32 values (soft cap of the logits). */
 int tb_tanh_cap(float* x, int64_t n, float cap, tb_stream_t stream);
 
-/* Gated feed-forward activation with clamps: g = min(gu[n, j], limit), u = clamp(gu[n, ff + j], -limit, limit),
- * out[n, j] = g * sigmoid(alpha * g) * (u + up_shift).  limit <= 0: no clamp.  gu fp32 [rows, 2 ff]. */
-int tb_gated_act(void* out, int out_dtype, const float* gu, int rows, int ff, float alpha, float limit, float up_shift,
-                 tb_stream_t stream);
+/* Gated feed-forward activation `gate` (TB_GATE_*) of g = gu[n, j], u = gu[n, ff + j]; gu fp32 [rows, 2 ff].
+ * row_scale != NULL: g and u of row n are first multiplied by row_scale[row_index ? row_index[n] : n] (0 where the index is
+ * negative): an expert whose router score weighs its input — the projections are linear, so the score moves behind them. */
+int tb_gated_act(void* out, int out_dtype, const float* gu, int rows, int ff, int gate, float alpha, float limit, float up_shift,
+                 const float* row_scale, const int* row_index, tb_stream_t stream);
 
 /* cos / sin of pos * base^(-2 i / dims), i < dims / 2, for every row: table fp32 [N, dims / 2, 2] (angles in fp64). */
 int tb_rope_table(float* table, const int* tok_pos, int rows, int dims, double base, tb_stream_t stream);
@@ -178,6 +206,19 @@ int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const float* pro
                             const int* block_table, int max_blocks, int page, int rows, int heads, int kv_heads, int dim,
                             int vdim, int taps, float* state_rw, const int* seq_len, tb_stream_t stream);
 
+/* The same step for an attention that RMS-normalises queries and keys over the WHOLE projection: proj holds q (heads * dim) | k
+ * (kv_heads * dim) [| v (kv_heads * vdim) unless tied_values].  After the convolution (conv_w [C, taps] or NULL: none) the q part
+ * and the k part are each divided by their root mean square over all their channels (eps inside the root) and multiplied by
+ * norm_q [heads * dim] / norm_k [kv_heads * dim] (both NULL: no norm), then rotated and stored as above.  tied_values != 0: the
+ * values are the keys as they leave the convolution, before norm and rotation (vdim == dim; C = (heads + kv_heads) * dim).
+ * The carried inputs are [slots, taps - 1, C]; carry them on as above. */
+int tb_qk_conv_norm_rope_append(void* q_out, void* pool, int dtype, const float* proj, int64_t ldp, const void* conv_w,
+                                const void* norm_q, const void* norm_k, int w_dtype, float eps, const float* state, const float* table,
+                                int dims, const int* tok_seq, const int* tok_pos, const int* seq_start, const int* seq_past,
+                                const int* seq_slot, const int* block_table, int max_blocks, int page, int rows, int heads,
+                                int kv_heads, int dim, int vdim, int taps, int tied_values, float* state_rw, const int* seq_len,
+                                tb_stream_t stream);
+
 /* Attention of every row over the cached positions j of its sequence with 0 <= pos - j < window (window 0: all of
  * 0..pos).  Query head h uses key/value head h / (heads / kv_heads).  score = scale * <q, k>; the softmax denominator
  * also holds exp(sink[h]) (sink fp32 or bf16 [heads], or NULL for none): a term without key or value, not scaled.
@@ -200,14 +241,15 @@ int tb_window_attention(void* out, const void* q, const void* pool, int dtype, c
 /* The same attention with value heads shared by neighbouring key heads: there are kv_heads key heads but only kv_heads / v_share
  * value heads, key head g reads value head g / v_share, and a pool entry is [kv_heads][dim] keys, then [kv_heads / v_share][vdim]
  * values (several attention maps over one set of values).  out_f32 != 0: the result is stored as fp32 [N, heads, vdim] whatever
- * the storage type (for a step that combines maps before anything is rounded).  v_share = 1, out_f32 = 0 is
- * tb_window_attention. */
+ * the storage type (for a step that combines maps before anything is rounded).  keep_first > 0 (with a window): positions
+ * j < keep_first stay visible to every later row as well (they keep their true positions).  v_share = 1, out_f32 = 0,
+ * keep_first = 0 is tb_window_attention. */
 int tb_window_attention_shared_values(void* out, int out_f32, const void* q, const void* pool, int dtype, const float* gate,
                                       int64_t ldg, const void* sink, int sink_dtype, const int* tok_seq, const int* tok_pos,
                                       const int* block_table, const int* seq_start, const int* seq_len, const int* seq_past,
                                       int seqs, int max_len, int max_blocks, int page, int rows, int heads, int kv_heads,
-                                      int v_share, int dim, int vdim, float scale, int window, int mode, int nsplit,
-                                      float* workspace, tb_stream_t stream);
+                                      int v_share, int dim, int vdim, float scale, int window, int keep_first, int mode,
+                                      int nsplit, float* workspace, tb_stream_t stream);
 
 /* ---- differential attention: two attention maps per head over one set of values ---------------------------------------
  * tb_qk_norm_append: proj fp32 [N, ldp] holds per row q_vectors query vectors, k_vectors key vectors (each of `dim`) and
@@ -256,6 +298,39 @@ int tb_delta_scan_set_mode(int mode);
 int tb_gated_rmsnorm_heads(void* out, int dtype, const float* o, const float* gate, int64_t ldg, const void* w, int w_dtype, float eps,
                            int rows, int heads, int vdim, tb_stream_t stream);
 
+/* ---- linear attention with a scalar decay per head and token ------------------------------------------------------------
+ * Per (sequence, head) a state S [dim, vcols] (fp32):  S_t = a_t S_(t-1) + b_t k_t v_t^T,  o_t = S_t^T q_t.
+ * q, k fp32 rows of [heads, dim] (row strides ldq, ldk), v fp32 rows of [heads, vdim] (ldv).  log_ab fp32 [N, heads, 2] = ln a_t
+ * (<= 0), ln b_t; or NULL, then a_t = head_decay[h] (fp32 [heads]) and b_t = 1.  ones_col != 0: one more value column follows
+ * the values whose v is 1 at every row (its state is sum of weighted keys: the normaliser of an mLSTM), vcols = vdim + 1.
+ * state: slot s at state + s * state_stride, [heads, vcols, dim] (a column's dim elements contiguous); zeros at a sequence's
+ * first position.  out fp32 [N, heads, vcols].  max_len: the longest seq_len (host): from 4 rows on (dim <= 256) the rows are
+ * resolved 32 at a time from the portion's first row (the same recurrence up to fp32 rounding), else row by row. */
+int tb_decay_attention_scan(float* out, const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
+                            const float* log_ab, const float* head_decay, float* state, int64_t state_stride, const int* seq_start,
+                            const int* seq_len, const int* seq_past, const int* seq_slot, int rows, int seqs, int heads, int dim,
+                            int vdim, int ones_col, int max_len, tb_stream_t stream);
+/* A/B switch for tests and measurements: 1 keeps tb_decay_attention_scan row by row; 0: by max_len (default). */
+int tb_decay_scan_set_mode(int mode);
+/* Gates of an mLSTM matrix memory.  Per row and head, from proj (fp32, row stride ldp): i = cap * tanh((proj[col_i + h] + bias_i[h])
+ * / cap), f = logsigmoid(cap * tanh((proj[col_f + h] + bias_f[h]) / cap)) (cap <= 0: no cap); running maximum m_t = max(f_t +
+ * m_(t-1), i_t) with m = 0 before a sequence's first row, carried in m_state[slot * m_stride + h].
+ * log_ab [N, heads, 2] = (f_t + m_(t-1) - m_t, i_t - m_t);  m_out [N, heads] = m_t. */
+int tb_mlstm_gates(float* log_ab, float* m_out, const float* proj, int64_t ldp, int col_i, int col_f, const void* bias_i,
+                   const void* bias_f, int w_dtype, float cap, float* m_state, int64_t m_stride, const int* seq_start,
+                   const int* seq_len, const int* seq_past, const int* seq_slot, int seqs, int heads, tb_stream_t stream);
+/* out fp32 rows of [heads, dim] (row stride ldo) = x (ldx) with the first `dims` elements of every head rotated by the row's table
+ * entry (tb_rope_table), pairs by `layout` (TB_ROPE_*), the rest copied; heads below `split` times scale_lo, the others times
+ * scale_hi.  out may be x. */
+int tb_rope_heads(float* out, int64_t ldo, const float* x, int64_t ldx, const float* table, int rows, int heads, int dim, int dims,
+                  int layout, int split, float scale_lo, float scale_hi, tb_stream_t stream);
+/* out T [N, heads, vdim] from o fp32 [N, heads, vcols] (the first vdim columns): with m (fp32 [N, heads]) first o / (max(|o[vdim]|,
+ * exp(-m)) + den_eps); then o / sqrt(mean_vdim(o^2) + eps) * w (w [vdim] shared, or [heads * vdim] when w_per_head; NULL: none)
+ * * act(gate) (gate fp32 logits [N, >= heads * vdim], row stride ldg; gate_act 0 none, 1 silu, 2 sigmoid). */
+int tb_head_norm_gate(void* out, int dtype, const float* o, int vcols, const float* m, float den_eps, const float* gate, int64_t ldg,
+                      int gate_act, const void* w, int w_dtype, int w_per_head, float eps, int rows, int heads, int vdim,
+                      tb_stream_t stream);
+
 /* ---- routed-expert feed-forward ------------------------------------------------------------------------------------
  * tb_moe_route: logits fp32 [N, experts].  s = sigmoid(logit); choice = s + correction (fp32 or bf16 [experts], NULL:
  * none).  Experts form `groups` equal groups of neighbours; a group scores the sum of its two largest choices and only the
@@ -290,12 +365,14 @@ int tb_moe_gather_rows(void* xs, const void* x, int x_dtype, int64_t ldx, const 
                        tb_stream_t stream);
 /* Expert products for few pairs (generation steps) without a plan: pair b = one row of the streaming kernel against the
  * weights of expert ids[b].  a_div > 0: a [tokens, K], pair b reads row b / a_div; a_div == 0: a [pairs, K].  c [pairs, N].
- * act TB_ACT_GATED: w [experts, 2 N, K] (gate rows, then up rows), c = g * sigmoid(alpha g) * (u + up_shift).
+ * act TB_ACT_GATED: w [experts, 2 N, K] (gate rows, then up rows), c = the gated activation `gate` (TB_GATE_*) of them, both
+ * first multiplied by pair_scale[b] when that is given (a score that weighs the expert's input).
  * Returns -3 when the streaming kernel does not take the shape (bf16 weights, 8 | K, 16-byte aligned rows). */
 int tb_moe_gemv(void* c, int c_dtype, int64_t ldc, const void* a, int a_dtype, int64_t lda, const void* w, int w_dtype,
-                const int* ids, int pairs, int a_div, int N, int K, int act, float alpha, float up_shift, tb_stream_t stream);
+                const int* ids, int pairs, int a_div, int N, int K, int act, int gate, float alpha, float limit, float up_shift,
+                const float* pair_scale, tb_stream_t stream);
 /* out fp32 [N, width] = sum_k weights[n, k] * y[r(n * top + k), :], k in index order; r(p) = pair_slot[p] (rows of y in
- * plan order) or p itself when pair_slot is NULL (y fp32 in pair order). */
+ * plan order) or p itself when pair_slot is NULL (y fp32 in pair order).  weights == NULL: a plain sum. */
 int tb_moe_combine(float* out, const float* y, const float* weights, const int* pair_slot, int rows, int width, int top,
                    tb_stream_t stream);
 

@@ -182,7 +182,7 @@ SIGNATURES.update({
 f64 = C.c_double
 RAGGED_SIGNATURES = {
     "tb_linear": (i32, [vp, i32, i64, i64, vp, i32, i64, i64, vp, i32, i64, vp, i64, i32, i32, i32, i32, i32, i32, vp]),
-    "tb_linear_gated": (i32, [vp, i32, i64, vp, i32, i64, vp, i32, i32, i32, i32, f32, f32, f32, vp]),
+    "tb_linear_gated": (i32, [vp, i32, i64, vp, i32, i64, vp, i32, i32, i32, i32, i32, f32, f32, f32, vp]),
     "tb_gemm_tc_bf16": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, i32, vp, sz, vp, vp]),
     "tb_cast_rows_bf16": (i32, [vp, vp, i64, i32, i32, vp]),
     "tb_embed_scaled": (i32, [vp, vp, i32, vp, f32, i32, i32, i32, vp]),
@@ -190,7 +190,7 @@ RAGGED_SIGNATURES = {
     "tb_residual_norm_rows": (i32, [vp, i64, vp, i64, vp, vp, i32, f32, f32, f32, vp, i32, i64, i32, i32, vp]),
     "tb_add_row_vector": (i32, [vp, i64, vp, i32, i32, i32, vp]),
     "tb_tanh_cap": (i32, [vp, i64, f32, vp]),
-    "tb_gated_act": (i32, [vp, i32, vp, i32, i32, f32, f32, f32, vp]),
+    "tb_gated_act": (i32, [vp, i32, vp, i32, i32, i32, f32, f32, f32, vp, vp, vp]),
     "tb_rope_table": (i32, [vp, vp, i32, i32, f64, vp]),
     "tb_rope_table_scaled": (i32, [vp, vp, i32, i32, f64, f64, f64, f64, f64, vp]),
     "tb_rope_query_tail": (i32, [vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
@@ -210,7 +210,7 @@ RAGGED_SIGNATURES = {
     "tb_moe_plan": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "tb_gemm_tc_bf16_grouped": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
     "tb_moe_gather_rows": (i32, [vp, vp, i32, i64, vp, i32, i32, i32, vp]),
-    "tb_moe_gemv": (i32, [vp, i32, i64, vp, i32, i64, vp, i32, vp, i32, i32, i32, i32, i32, f32, f32, vp]),
+    "tb_moe_gemv": (i32, [vp, i32, i64, vp, i32, i64, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, f32, f32, vp, vp]),
     "tb_moe_linear": (i32, [vp, i32, i64, vp, i32, i64, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]),
     "tb_moe_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
     "tb_moe_combine_add": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, vp]),
@@ -219,7 +219,19 @@ RAGGED_SIGNATURES = {
     "tb_residual_layernorm_rows": (i32, [vp, i64, vp, i64, vp, i64, f32, vp, vp, i32, f32, vp, i32, i64, i32, i32, vp]),
     "tb_concat_rows": (i32, [vp, i32, vp, i64, i32, vp, i64, i32, i32, vp]),
     "tb_window_attention_shared_values": (i32, [vp, i32, vp, vp, i32, vp, i64, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
-                                                i32, i32, i32, i32, i32, i32, f32, i32, i32, i32, vp, vp]),
+                                                i32, i32, i32, i32, i32, i32, f32, i32, i32, i32, i32, vp, vp]),
+    "tb_qk_conv_norm_rope_append": (i32, [vp, vp, i32, vp, i64, vp, vp, vp, i32, f32, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32,
+                                          i32, i32, i32, i32, i32, i32, i32, vp, vp, vp]),
+    "tb_embed_bigram": (i32, [vp, vp, vp, i32, vp, vp, f32, i32, i32, i32, i32, i32, i32, vp]),
+    "tb_residual_sandwich_layernorm_rows": (i32, [vp, i64, vp, i64, vp, vp, vp, vp, i32, f32, f32, vp, i32, i64, i32, i32, vp]),
+    "tb_token_side_input": (i32, [vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, f32, i32, i32, i32, vp, vp, i32, vp, i32, i64, vp]),
+    "tb_rmsnorm_pair_sum": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, i32, f32, f32, i32, i32, vp]),
+    "tb_decay_attention_scan": (i32, [vp, vp, i64, vp, i64, vp, i64, vp, vp, vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
+                                      i32, vp]),
+    "tb_decay_scan_set_mode": (i32, [i32]),
+    "tb_mlstm_gates": (i32, [vp, vp, vp, i64, i32, i32, vp, vp, i32, f32, vp, i64, vp, vp, vp, vp, i32, i32, vp]),
+    "tb_rope_heads": (i32, [vp, i64, vp, i64, vp, i32, i32, i32, i32, i32, i32, f32, f32, vp]),
+    "tb_head_norm_gate": (i32, [vp, i32, vp, i32, vp, f32, vp, i64, i32, vp, i32, i32, f32, i32, i32, i32, vp]),
     "tb_qk_norm_append": (i32, [vp, vp, i32, vp, i64, vp, vp, i32, f32, f32, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]),
     "tb_diff_combine": (i32, [vp, i32, vp, vp, vp, vp, vp, i32, i32, f32, f32, f32, i32, i32, i32, i32, vp]),
     "tb_delta_prepare": (i32, [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,

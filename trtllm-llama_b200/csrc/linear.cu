@@ -54,6 +54,9 @@ struct LinArgs {
   // (< 0: padding).  A row = pair / a_div when a_div > 0 (the token's row), else the slot; C row = the pair when
   // c_by_pair, else the slot.
   const int* tile_expert; const int* slot_pair; int a_div, c_by_pair;
+  // TB_ACT_GATED: which gated activation (TB_GATE_*), and an optional factor per batch element on gate and up before it (a
+  // routed expert whose score weighs its input: the pair's score, applied behind the linear projections)
+  int gate; const float* row_scale;
 };
 
 // row of A and of C behind tile row gm (-1: none)
@@ -395,6 +398,8 @@ __global__ void __launch_bounds__(256) linear_gemv_kernel(LinArgs p, int vec_a) 
         for (int m = 0; m < MR; ++m) {
           if (m >= p.M) break;
           float gq = acc[m], uq = up[m];
+          if (p.row_scale) { const float sc = p.row_scale[b]; gq *= sc; uq *= sc; }
+          if (p.gate == TB_GATE_GELU_TANH) { C[(int64_t) m * p.ldc + n] = from_f<CT>(gelu_tanh(gq) * uq); continue; }
           if (p.limit > 0.f) { gq = fminf(gq, p.limit); uq = fminf(fmaxf(uq, -p.limit), p.limit); }
           C[(int64_t) m * p.ldc + n] = from_f<CT>(gq * (1.f / (1.f + expf(-p.alpha * gq))) * (uq + p.up_shift));
         }
@@ -524,16 +529,16 @@ extern "C" int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const 
 }
 
 extern "C" int tb_linear_gated(void* c, int c_dtype, int64_t ldc, const void* a, int a_dtype, int64_t lda, const void* w,
-                               int w_dtype, int M, int ff, int K, float alpha, float limit, float up_shift,
+                               int w_dtype, int M, int ff, int K, int gate, float alpha, float limit, float up_shift,
                                tb_stream_t stream) {
   using namespace tb;
-  if (!c || !a || !w || ff <= 0 || K <= 0 || M < 0) return -1;
+  if (!c || !a || !w || ff <= 0 || K <= 0 || M < 0 || (gate != TB_GATE_SIGMOID && gate != TB_GATE_GELU_TANH)) return -1;
   if ((c_dtype != TB_DT_F32 && c_dtype != TB_DT_BF16) || (a_dtype != TB_DT_F32 && a_dtype != TB_DT_BF16)) return -1;
   if (M == 0) return 0;
   // the fused form exists for the streaming kernel only: the caller runs projection + activation otherwise
   const int mr = M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8));
   if (w_dtype != TB_DT_BF16 || M > 8 || K % 8 || (uintptr_t) w % 16 || (size_t) mr * K * 2 > 200 * 1024) return -3;
-  LinArgs p{c, a, w, nullptr, ldc, 0, lda, 0, 0, 0, M, ff, K, TB_ACT_GATED, alpha, limit, up_shift};
+  LinArgs p{c, a, w, nullptr, ldc, 0, lda, 0, 0, 0, M, ff, K, TB_ACT_GATED, alpha, limit, up_shift, nullptr, nullptr, 0, 0, gate, nullptr};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   int rc;
   if (a_dtype == TB_DT_F32) rc = c_dtype == TB_DT_F32 ? launch_gemv<float, float>(p, 1, s) : launch_gemv<float, __nv_bfloat16>(p, 1, s);
@@ -586,11 +591,12 @@ extern "C" int tb_moe_linear(void* c, int c_dtype, int64_t ldc, const void* a, i
 // Expert products for a handful of (token, choice) pairs (generation steps): pair b is one single-row product of the
 // streaming kernel against expert ids[b]'s weights, so only the chosen experts' weights are read and no plan is needed.
 // a_div > 0: a [tokens, K], pair b reads row b / a_div; a_div == 0: a [pairs, K].  c [pairs, N] in pair order.
-// act TB_ACT_GATED: w holds per expert N gate rows, then N up rows; c = g * sigmoid(alpha g) * (u + up_shift), no clamp.
+// act TB_ACT_GATED: w holds per expert N gate rows, then N up rows; c = the gated activation `gate` (TB_GATE_*) of them, both
+// first multiplied by pair_scale[b] when that is given.
 // Returns -3 when the shape is not one the streaming kernel takes.
 extern "C" int tb_moe_gemv(void* c, int c_dtype, int64_t ldc, const void* a, int a_dtype, int64_t lda, const void* w, int w_dtype,
-                           const int* ids, int pairs, int a_div, int N, int K, int act, float alpha, float up_shift,
-                           tb_stream_t stream) {
+                           const int* ids, int pairs, int a_div, int N, int K, int act, int gate, float alpha, float limit,
+                           float up_shift, const float* pair_scale, tb_stream_t stream) {
   using namespace tb;
   auto ok = [](int d) { return d == TB_DT_F32 || d == TB_DT_BF16; };
   if (!c || !a || !w || !ids || !ok(c_dtype) || !ok(a_dtype) || N <= 0 || K <= 0 || pairs < 0 || a_div < 0) return -1;
@@ -600,7 +606,9 @@ extern "C" int tb_moe_gemv(void* c, int c_dtype, int64_t ldc, const void* a, int
       (uintptr_t) a % 16)
     return -3;
   const int64_t w_bs = (int64_t) (act == TB_ACT_GATED ? 2 : 1) * N * K;
-  LinArgs p{c, a, w, nullptr, ldc, ldc, lda, lda, w_bs, 0, 1, N, K, act, alpha, 0.f, up_shift, ids, nullptr, a_div, 0};
+  if (act == TB_ACT_GATED && gate != TB_GATE_SIGMOID && gate != TB_GATE_GELU_TANH) return -1;
+  LinArgs p{c, a, w, nullptr, ldc, ldc, lda, lda, w_bs, 0, 1, N, K, act, alpha, limit, up_shift, ids, nullptr, a_div, 0, gate,
+            act == TB_ACT_GATED ? pair_scale : nullptr};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   int rc;
   if (a_dtype == TB_DT_F32) rc = c_dtype == TB_DT_F32 ? launch_gemv<float, float>(p, pairs, s) : launch_gemv<float, __nv_bfloat16>(p, pairs, s);

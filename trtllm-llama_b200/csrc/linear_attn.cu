@@ -1,0 +1,458 @@
+// Linear attention with a scalar decay per head and token over a ragged in-flight batch — the recurrence behind a retention
+// (fixed decay per head) and behind the matrix memory of an mLSTM (decay and input weight from exponential gates kept in range
+// by a running maximum) — with the steps around it: rotation of projected heads in either pairing, the gates of the matrix
+// memory, and the per-head normalisation + output gate.
+//
+//   S_t = a_t S_(t-1) + b_t k_t v_t^T,   o_t = S_t^T q_t          S [dim, vcols] fp32 per (sequence, head)
+//
+// Everything here is fp32: the state, the decays and their logarithms, the products that enter the state.
+//
+//   rope_heads_kernel        a thread per rotated pair: (2i, 2i + 1) or (i, i + dims / 2), with an output factor per head range
+//   mlstm_gates_kernel       a warp per (sequence, head): capped gates, then the running maximum m_t = max(f_t + m_(t-1), i_t) as a
+//                            max-plus prefix scan over 32 rows at a time; emits ln a_t = f_t + m_(t-1) - m_t, ln b_t = i_t - m_t, m_t
+//   decay_scan_rows_kernel   row by row, a warp per value column with dim over its lanes (generation steps, any dim <= 1024)
+//   decay_scan_chunk_kernel  prompt portions, 32 rows at a time: the chunk's own products A[t, s] = (q_t . k_s) a_(s+1..t) b_s, then
+//                            o = a_(..t) S0^T q_t + A V and S <- a_(..n) S0 + K^T (w V) as register-tiled fp32 products: a thread owns
+//                            one value column and an eighth of dim, partial read-outs meet in shared memory
+//   head_norm_gate_kernel    a warp per (row, head): optional division by max(|n . q|, exp(-m)) + tiny, RMS norm over vdim, weight,
+//                            silu or sigmoid gate
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "../../include/trtllm_b200_ragged.h"
+
+namespace tb {
+namespace {
+
+__device__ __forceinline__ float ld_w(const void* p, int dtype, int64_t i) {
+  return dtype == TB_DT_F32 ? reinterpret_cast<const float*>(p)[i]
+                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void rope_heads_kernel(float* out, int64_t ldo, const float* x, int64_t ldx, const float* table, int rows, int heads,
+                                  int dim, int dims, int layout, int split, float scale_lo, float scale_hi) {
+  const int half = dims / 2, rest = dim - dims;
+  const int per_head = half + rest;                       // work items of a head: rotated pairs, then untouched elements
+  const int64_t n = (int64_t) rows * heads * per_head;
+  for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
+    const int w = (int) (i % per_head);
+    const int h = (int) ((i / per_head) % heads);
+    const int64_t row = i / ((int64_t) per_head * heads);
+    const float sc = h < split ? scale_lo : scale_hi;
+    const float* src = x + row * ldx + (int64_t) h * dim;
+    float* dst = out + row * ldo + (int64_t) h * dim;
+    if (w >= half) { dst[dims + w - half] = src[dims + w - half] * sc; continue; }
+    const int i0 = layout == TB_ROPE_HALF ? w : 2 * w, i1 = layout == TB_ROPE_HALF ? w + half : 2 * w + 1;
+    const float c = table[(row * half + w) * 2], s = table[(row * half + w) * 2 + 1];
+    const float u = src[i0], v = src[i1];
+    dst[i0] = fmaf(u, c, -v * s) * sc;
+    dst[i1] = fmaf(v, c, u * s) * sc;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+struct GateArgs {
+  const float* proj; int64_t ldp; int col_i, col_f;
+  const void *bias_i, *bias_f; int w_dtype; float cap;
+  float* m_state; int64_t m_stride;                 // running maximum per (slot, head): m_state[slot * m_stride + head]
+  const int *seq_start, *seq_len, *seq_past, *seq_slot;
+  int heads;
+};
+
+__device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+__global__ void __launch_bounds__(32) mlstm_gates_kernel(float* log_ab, float* m_out, GateArgs a) {
+  const int h = blockIdx.x, e = blockIdx.y, lane = threadIdx.x;
+  const int len = a.seq_len[e], start = a.seq_start[e], past = a.seq_past[e];
+  float* ms = a.m_state + (int64_t) a.seq_slot[e] * a.m_stride + h;
+  float m = past > 0 ? *ms : 0.f;                      // the maximum starts at 0, not at -inf
+  const float bi = a.bias_i ? ld_w(a.bias_i, a.w_dtype, h) : 0.f, bf = a.bias_f ? ld_w(a.bias_f, a.w_dtype, h) : 0.f;
+  for (int c0 = 0; c0 < len; c0 += 32) {
+    const int t = c0 + lane;
+    const bool live = t < len;
+    float ig = -INFINITY, fg = 0.f;                    // a dead lane is the identity map m -> max(m + 0, -inf)
+    if (live) {
+      const float* pr = a.proj + (int64_t) (start + t) * a.ldp;
+      float zi = pr[a.col_i + h] + bi, zf = pr[a.col_f + h] + bf;
+      if (a.cap > 0.f) { zi = a.cap * tanhf(zi / a.cap); zf = a.cap * tanhf(zf / a.cap); }
+      ig = zi;
+      fg = log_sigmoid(zf);
+    }
+    // inclusive max-plus scan: lane t ends with the map of rows c0..t in a row, m -> max(m + F, I)
+    float F = fg, I = ig;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float Fp = __shfl_up_sync(0xffffffffu, F, o), Ip = __shfl_up_sync(0xffffffffu, I, o);
+      if (lane >= o) { I = fmaxf(Ip + F, I); F = Fp + F; }
+    }
+    const float mt = fmaxf(m + F, I);
+    float mp = __shfl_up_sync(0xffffffffu, mt, 1);
+    if (lane == 0) mp = m;
+    if (live) {
+      const int64_t o = (int64_t) (start + t) * a.heads + h;
+      log_ab[2 * o] = fg + mp - mt;
+      log_ab[2 * o + 1] = ig - mt;
+      m_out[o] = mt;
+    }
+    m = __shfl_sync(0xffffffffu, mt, 31);
+  }
+  if (lane == 0) *ms = m;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+struct ScanArgs {
+  const float *q, *k, *v; int64_t ldq, ldk, ldv;      // rows of [heads, dim] / [heads, vdim] behind these strides
+  const float* log_ab;                                // [rows, heads, 2] or NULL
+  const float* head_decay;                            // [heads] when log_ab is NULL
+  float* state; int64_t state_stride;                 // state + slot * state_stride: [heads, vcols, dim]
+  const int *seq_start, *seq_len, *seq_past, *seq_slot;
+  int heads, dim, vdim, vcols;                        // vcols = vdim + 1 when a column of ones follows the values
+};
+
+constexpr int kRowWarps = 4;
+
+template <int DPL>
+__global__ void __launch_bounds__(kRowWarps * 32) decay_scan_rows_kernel(float* out, ScanArgs a) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int col = blockIdx.x * kRowWarps + warp, h = blockIdx.y, e = blockIdx.z;
+  if (col >= a.vcols) return;
+  const int len = a.seq_len[e], start = a.seq_start[e], past = a.seq_past[e];
+  float* sp = a.state + (int64_t) a.seq_slot[e] * a.state_stride + ((int64_t) h * a.vcols + col) * a.dim;
+  float s[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) {
+    const int d = lane + 32 * i;
+    s[i] = past > 0 && d < a.dim ? sp[d] : 0.f;
+  }
+  const float fixed = a.log_ab ? 0.f : a.head_decay[h];
+  for (int t = 0; t < len; ++t) {
+    const int64_t row = start + t;
+    float at = fixed, bt = 1.f;
+    if (a.log_ab) { at = expf(a.log_ab[2 * (row * a.heads + h)]); bt = expf(a.log_ab[2 * (row * a.heads + h) + 1]); }
+    const float vv = (col < a.vdim ? a.v[row * a.ldv + (int64_t) h * a.vdim + col] : 1.f) * bt;
+    const float* qr = a.q + row * a.ldq + (int64_t) h * a.dim;
+    const float* kr = a.k + row * a.ldk + (int64_t) h * a.dim;
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      const int d = lane + 32 * i;
+      if (d < a.dim) {
+        s[i] = fmaf(at, s[i], vv * kr[d]);
+        o = fmaf(s[i], qr[d], o);
+      }
+    }
+    o = warp_sum(o);
+    if (lane == 0) out[(row * a.heads + h) * a.vcols + col] = o;
+  }
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) {
+    const int d = lane + 32 * i;
+    if (d < a.dim) sp[d] = s[i];
+  }
+}
+
+// Prompt portions, 32 rows at a time.  CTA = (32 value columns, head, sequence), 8 warps: lane = column, warp = an eighth of
+// dim (DPT elements, dim padded to 8 DPT with zeros).  Shared memory (floats):
+//   Q [32][LD] | K [32][LD] | V [32][32] | A [32][33] | part [8][32][32] | L [32] | lbs [32] | eL [32] | wS [32]      LD = 8 DPT + 4
+constexpr int kChunk = 32;
+
+template <int DPT>
+__global__ void __launch_bounds__(256) decay_scan_chunk_kernel(float* out, ScanArgs a) {
+  constexpr int DP = 8 * DPT, LD = DP + 4;
+  extern __shared__ __align__(16) float sm[];
+  float* Qs = sm;
+  float* Ks = Qs + kChunk * LD;
+  float* Vs = Ks + kChunk * LD;
+  float* As = Vs + kChunk * 32;
+  float* part = As + kChunk * 33;
+  float* Ls = part + 8 * kChunk * 32;
+  float* lbs = Ls + kChunk;
+  float* eL = lbs + kChunk;
+  float* wS = eL + kChunk;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int cg = blockIdx.x, h = blockIdx.y, e = blockIdx.z;
+  const int len = a.seq_len[e], start = a.seq_start[e], past = a.seq_past[e];
+  const int col = cg * 32 + lane;
+  const bool col_ok = col < a.vcols;
+  float* sp = a.state + (int64_t) a.seq_slot[e] * a.state_stride + ((int64_t) h * a.vcols + (col_ok ? col : 0)) * a.dim;
+  float s[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const int d = warp * DPT + i;
+    s[i] = past > 0 && col_ok && d < a.dim ? sp[d] : 0.f;
+  }
+  const float fixed_la = a.log_ab ? 0.f : logf(a.head_decay[h]);
+  for (int c0 = 0; c0 < len; c0 += kChunk) {
+    const int n = min(kChunk, len - c0);
+    const int64_t row0 = start + c0;
+    __syncthreads();                                   // the previous chunk's tiles have been consumed
+    for (int idx = threadIdx.x; idx < kChunk * DP; idx += 256) {
+      const int t = idx / DP, d = idx % DP;
+      const bool ok = t < n && d < a.dim;
+      Qs[t * LD + d] = ok ? a.q[(row0 + t) * a.ldq + (int64_t) h * a.dim + d] : 0.f;
+      Ks[t * LD + d] = ok ? a.k[(row0 + t) * a.ldk + (int64_t) h * a.dim + d] : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < kChunk * 32; idx += 256) {
+      const int t = idx / 32, c = cg * 32 + idx % 32;
+      float v = 0.f;
+      if (t < n && c < a.vcols) v = c < a.vdim ? a.v[(row0 + t) * a.ldv + (int64_t) h * a.vdim + c] : 1.f;
+      Vs[idx] = v;
+    }
+    if (warp == 0) {
+      float la = 0.f, lb = -INFINITY;
+      if (lane < n) {
+        if (a.log_ab) { la = a.log_ab[2 * ((row0 + lane) * a.heads + h)]; lb = a.log_ab[2 * ((row0 + lane) * a.heads + h) + 1]; }
+        else { la = fixed_la; lb = 0.f; }
+      }
+      float L = la;                                    // inclusive sum of ln a over the chunk's rows
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float p = __shfl_up_sync(0xffffffffu, L, o);
+        if (lane >= o) L += p;
+      }
+      const float Ltot = __shfl_sync(0xffffffffu, L, n - 1);
+      Ls[lane] = L;
+      lbs[lane] = lb - L;                              // weight of key s for row t: exp(L_t - L_s + ln b_s)
+      eL[lane] = expf(L);                              // weight of the carried state for row t
+      wS[lane] = lane < n ? expf(Ltot - L + lb) : 0.f;  // weight of key s in the state after the chunk
+    }
+    __syncthreads();
+    // the chunk's own products: thread -> rows t = warp * 4 + j, key s = lane
+    {
+      float dot[4] = {0.f, 0.f, 0.f, 0.f};
+      const float* kr = Ks + lane * LD;
+#pragma unroll 4
+      for (int d = 0; d < DP; d += 4) {
+        const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 qv = *reinterpret_cast<const float4*>(Qs + (warp * 4 + j) * LD + d);
+          dot[j] = fmaf(qv.x, kv.x, dot[j]);
+          dot[j] = fmaf(qv.y, kv.y, dot[j]);
+          dot[j] = fmaf(qv.z, kv.z, dot[j]);
+          dot[j] = fmaf(qv.w, kv.w, dot[j]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = warp * 4 + j;
+        As[t * 33 + lane] = (lane <= t && t < n) ? dot[j] * expf(Ls[t] + lbs[lane]) : 0.f;
+      }
+    }
+    __syncthreads();
+    float acc[kChunk];
+#pragma unroll
+    for (int t = 0; t < kChunk; ++t) {
+      float p = 0.f;
+      const float* qr = Qs + t * LD + warp * DPT;
+      if constexpr (DPT % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < DPT; i += 4) {
+          const float4 qv = *reinterpret_cast<const float4*>(qr + i);
+          p = fmaf(s[i], qv.x, p); p = fmaf(s[i + 1], qv.y, p); p = fmaf(s[i + 2], qv.z, p); p = fmaf(s[i + 3], qv.w, p);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < DPT; i += 2) {
+          const float2 qv = *reinterpret_cast<const float2*>(qr + i);
+          p = fmaf(s[i], qv.x, p); p = fmaf(s[i + 1], qv.y, p);
+        }
+      }
+      acc[t] = p * eL[t];
+    }
+    for (int sk = warp; sk < n; sk += 8) {             // this warp's share of the chunk's keys
+      const float vv = Vs[sk * 32 + lane];
+#pragma unroll
+      for (int t = 0; t < kChunk; ++t) acc[t] = fmaf(As[t * 33 + sk], vv, acc[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < kChunk; ++t) part[(warp * kChunk + t) * 32 + lane] = acc[t];
+    // the state after the chunk
+    const float dec = eL[n - 1];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) s[i] *= dec;
+    for (int sk = 0; sk < n; ++sk) {
+      const float wv = wS[sk] * Vs[sk * 32 + lane];
+      const float* kr = Ks + sk * LD + warp * DPT;
+      if constexpr (DPT % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < DPT; i += 4) {
+          const float4 kv = *reinterpret_cast<const float4*>(kr + i);
+          s[i] = fmaf(wv, kv.x, s[i]); s[i + 1] = fmaf(wv, kv.y, s[i + 1]); s[i + 2] = fmaf(wv, kv.z, s[i + 2]); s[i + 3] = fmaf(wv, kv.w, s[i + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < DPT; i += 2) {
+          const float2 kv = *reinterpret_cast<const float2*>(kr + i);
+          s[i] = fmaf(wv, kv.x, s[i]); s[i + 1] = fmaf(wv, kv.y, s[i + 1]);
+        }
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < kChunk * 32; idx += 256) {
+      const int t = idx / 32, c = idx % 32;
+      if (t >= n || cg * 32 + c >= a.vcols) continue;
+      float o = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) o += part[(w * kChunk + t) * 32 + c];      // fixed order
+      out[((row0 + t) * a.heads + h) * a.vcols + cg * 32 + c] = o;
+    }
+  }
+  if (col_ok) {
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int d = warp * DPT + i;
+      if (d < a.dim) sp[d] = s[i];
+    }
+  }
+}
+
+template <int DPT>
+int launch_chunk(float* out, const ScanArgs& a, int seqs, cudaStream_t st) {
+  constexpr int DP = 8 * DPT, LD = DP + 4;
+  constexpr size_t smem = ((size_t) 2 * kChunk * LD + kChunk * 32 + kChunk * 33 + 8 * kChunk * 32 + 4 * kChunk) * sizeof(float);
+  static bool raised = false;
+  if (!raised && smem > 48 * 1024) {
+    TB_CHECK_CUDA(cudaFuncSetAttribute(decay_scan_chunk_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    raised = true;
+  }
+  dim3 grid((a.vcols + 31) / 32, a.heads, seqs);
+  decay_scan_chunk_kernel<DPT><<<grid, 256, smem, st>>>(out, a);
+  return 0;
+}
+
+template <int DPL>
+void launch_rows(float* out, const ScanArgs& a, int seqs, cudaStream_t st) {
+  dim3 grid((a.vcols + kRowWarps - 1) / kRowWarps, a.heads, seqs);
+  decay_scan_rows_kernel<DPL><<<grid, kRowWarps * 32, 0, st>>>(out, a);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+struct HeadNormArgs {
+  const float* o; int vcols;                         // [rows, heads, vcols]; the first vdim columns are the read-out
+  const float* m;                                    // [rows, heads] running maxima, or NULL: no division
+  float den_eps;
+  const float* gate; int64_t ldg; int gate_act;      // logits [rows, >= heads * vdim]; 0 none, 1 silu, 2 sigmoid
+  const void* w; int w_dtype; int w_per_head;        // [vdim] shared by the heads, or [heads * vdim]
+  float eps; int rows, heads, vdim;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) head_norm_gate_kernel(T* out, HeadNormArgs a) {
+  const int lane = threadIdx.x % 32;
+  const int64_t item = (int64_t) blockIdx.x * 4 + threadIdx.x / 32;
+  if (item >= (int64_t) a.rows * a.heads) return;
+  const int h = (int) (item % a.heads);
+  const int64_t row = item / a.heads;
+  const float* src = a.o + item * a.vcols;
+  float f = 1.f;
+  if (a.m) f = 1.f / (fmaxf(fabsf(src[a.vdim]), expf(-a.m[item])) + a.den_eps);
+  float ss = 0.f;
+  for (int c = lane; c < a.vdim; c += 32) { const float v = src[c] * f; ss = fmaf(v, v, ss); }
+  ss = warp_sum(ss);
+  const float inv = f / sqrtf(ss / (float) a.vdim + a.eps);
+  for (int c = lane; c < a.vdim; c += 32) {
+    float v = src[c] * inv;
+    if (a.w) v *= ld_w(a.w, a.w_dtype, a.w_per_head ? (int64_t) h * a.vdim + c : c);
+    if (a.gate_act) {
+      const float z = a.gate[row * a.ldg + (int64_t) h * a.vdim + c], sg = 1.f / (1.f + expf(-z));
+      v *= a.gate_act == 1 ? z * sg : sg;
+    }
+    out[item * a.vdim + c] = from_f<T>(v);
+  }
+}
+
+}  // namespace
+}  // namespace tb
+
+using namespace tb;
+
+extern "C" int tb_rope_heads(float* out, int64_t ldo, const float* x, int64_t ldx, const float* table, int rows, int heads, int dim,
+                             int dims, int layout, int split, float scale_lo, float scale_hi, tb_stream_t stream) {
+  if (!out || !x || rows < 0 || heads <= 0 || dim <= 0 || dims < 0 || dims % 2 || dims > dim || (dims > 0 && !table) ||
+      (layout != TB_ROPE_INTERLEAVED && layout != TB_ROPE_HALF))
+    return -1;
+  if (rows == 0) return 0;
+  const int64_t n = (int64_t) rows * heads * (dim - dims / 2);
+  const int grid = (int) std::min<int64_t>((n + 255) / 256, 148 * 16);
+  rope_heads_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(out, ldo, x, ldx, table, rows, heads, dim, dims, layout, split, scale_lo,
+                                                             scale_hi);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_mlstm_gates(float* log_ab, float* m_out, const float* proj, int64_t ldp, int col_i, int col_f, const void* bias_i,
+                              const void* bias_f, int w_dtype, float cap, float* m_state, int64_t m_stride, const int* seq_start,
+                              const int* seq_len, const int* seq_past, const int* seq_slot, int seqs, int heads, tb_stream_t stream) {
+  if (!log_ab || !m_out || !proj || !m_state || !seq_start || !seq_len || !seq_past || !seq_slot || heads <= 0 || seqs < 0 ||
+      col_i < 0 || col_f < 0 || seqs > 65535)
+    return -1;
+  if ((bias_i || bias_f) && w_dtype != TB_DT_F32 && w_dtype != TB_DT_BF16) return -1;
+  if (seqs == 0) return 0;
+  GateArgs a{proj, ldp, col_i, col_f, bias_i, bias_f, w_dtype, cap, m_state, m_stride, seq_start, seq_len, seq_past, seq_slot, heads};
+  mlstm_gates_kernel<<<dim3(heads, seqs), 32, 0, (cudaStream_t) stream>>>(log_ab, m_out, a);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static int g_decay_scan_mode = 0;
+extern "C" int tb_decay_scan_set_mode(int mode) { g_decay_scan_mode = mode; return 0; }
+
+extern "C" int tb_decay_attention_scan(float* out, const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
+                                       const float* log_ab, const float* head_decay, float* state, int64_t state_stride,
+                                       const int* seq_start, const int* seq_len, const int* seq_past, const int* seq_slot, int rows,
+                                       int seqs, int heads, int dim, int vdim, int ones_col, int max_len, tb_stream_t stream) {
+  if (!out || !q || !k || !v || !state || !seq_start || !seq_len || !seq_past || !seq_slot || (!log_ab && !head_decay)) return -1;
+  if (heads <= 0 || dim <= 0 || dim > 1024 || vdim <= 0 || rows < 0 || seqs < 0 || seqs > 65535 || heads > 65535) return -1;
+  if (rows == 0 || seqs == 0) return 0;
+  ScanArgs a{q, k, v, ldq, ldk, ldv, log_ab, head_decay, state, state_stride, seq_start, seq_len, seq_past, seq_slot, heads, dim, vdim,
+             vdim + (ones_col ? 1 : 0)};
+  cudaStream_t st = (cudaStream_t) stream;
+  if (g_decay_scan_mode != 1 && max_len >= 4 && dim <= 256) {
+    const int dpt = (dim + 7) / 8;
+    int rc;
+    if (dpt <= 2) rc = launch_chunk<2>(out, a, seqs, st);
+    else if (dpt <= 4) rc = launch_chunk<4>(out, a, seqs, st);
+    else if (dpt <= 6) rc = launch_chunk<6>(out, a, seqs, st);
+    else if (dpt <= 8) rc = launch_chunk<8>(out, a, seqs, st);
+    else if (dpt <= 12) rc = launch_chunk<12>(out, a, seqs, st);
+    else if (dpt <= 16) rc = launch_chunk<16>(out, a, seqs, st);
+    else if (dpt <= 24) rc = launch_chunk<24>(out, a, seqs, st);
+    else rc = launch_chunk<32>(out, a, seqs, st);
+    if (rc) return rc;
+    TB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
+  const int dpl = (dim + 31) / 32;
+  if (dpl <= 1) launch_rows<1>(out, a, seqs, st);
+  else if (dpl <= 2) launch_rows<2>(out, a, seqs, st);
+  else if (dpl <= 4) launch_rows<4>(out, a, seqs, st);
+  else if (dpl <= 8) launch_rows<8>(out, a, seqs, st);
+  else if (dpl <= 16) launch_rows<16>(out, a, seqs, st);
+  else launch_rows<32>(out, a, seqs, st);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_head_norm_gate(void* out, int dtype, const float* o, int vcols, const float* m, float den_eps, const float* gate,
+                                 int64_t ldg, int gate_act, const void* w, int w_dtype, int w_per_head, float eps, int rows, int heads,
+                                 int vdim, tb_stream_t stream) {
+  if (!out || !o || (dtype != TB_DT_F32 && dtype != TB_DT_BF16) || rows < 0 || heads <= 0 || vdim <= 0 || vcols < vdim ||
+      (m && vcols < vdim + 1) || gate_act < 0 || gate_act > 2 || (gate_act && !gate))
+    return -1;
+  if (w && w_dtype != TB_DT_F32 && w_dtype != TB_DT_BF16) return -1;
+  if (rows == 0) return 0;
+  HeadNormArgs a{o, vcols, m, den_eps, gate, ldg, gate_act, w, w_dtype, w_per_head, eps, rows, heads, vdim};
+  const int64_t items = (int64_t) rows * heads;
+  const unsigned grid = (unsigned) ((items + 3) / 4);
+  if (dtype == TB_DT_F32) head_norm_gate_kernel<float><<<grid, 128, 0, (cudaStream_t) stream>>>((float*) out, a);
+  else head_norm_gate_kernel<__nv_bfloat16><<<grid, 128, 0, (cudaStream_t) stream>>>((__nv_bfloat16*) out, a);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

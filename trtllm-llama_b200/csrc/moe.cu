@@ -193,7 +193,7 @@ __global__ void moe_combine_kernel(float* out, const float* y, const float* weig
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
       const int64_t r = pair_slot ? pair_slot[row * top + k] : row * top + k;
-      if (r >= 0) acc = fmaf(weights[row * top + k], y[r * width + c], acc);
+      if (r >= 0) acc = weights ? fmaf(weights[row * top + k], y[r * width + c], acc) : acc + y[r * width + c];
     }
     out[i] = add ? acc + add[i] : acc;
   }
@@ -287,7 +287,7 @@ extern "C" int tb_moe_combine(float* out, const float* y, const float* weights, 
 
 extern "C" int tb_moe_combine_add(float* out, const float* y, const float* weights, const int* pair_slot, const float* add, int rows,
                                   int width, int top, tb_stream_t stream) {
-  if (!out || !y || !weights || rows < 0 || width <= 0 || top <= 0) return -1;
+  if (!out || !y || rows < 0 || width <= 0 || top <= 0) return -1;
   if (rows == 0) return 0;
   const int64_t n = (int64_t) rows * width;
   const int grid = (int) ((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);

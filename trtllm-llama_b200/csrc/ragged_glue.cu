@@ -177,16 +177,165 @@ __global__ void concat_rows_kernel(void* out, int out_dtype, const float* a, int
   }
 }
 
-__global__ void gated_act_kernel(void* out, int out_dtype, const float* gu, int64_t n, int ff, float alpha, float limit,
-                                 float up_shift) {
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// row_scale != NULL: gate and up values of row r are multiplied by row_scale[row_index ? row_index[r] : r] first (0 where the
+// index is negative) — a routed expert whose score weighs its INPUT: the projections are linear, so the score moves behind them
+__global__ void gated_act_kernel(void* out, int out_dtype, const float* gu, int64_t n, int ff, int gate, float alpha, float limit,
+                                 float up_shift, const float* row_scale, const int* row_index) {
   for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
     const int64_t row = i / ff;
     const int j = (int) (i % ff);
     float g = gu[row * 2 * ff + j], u = gu[row * 2 * ff + ff + j];
+    if (row_scale) {
+      const int64_t r = row_index ? row_index[row] : row;
+      const float sc = r >= 0 ? row_scale[r] : 0.f;
+      g *= sc;
+      u *= sc;
+    }
+    if (gate == TB_GATE_GELU_TANH) { st_f(out, out_dtype, i, gelu_tanh_f(g) * u); continue; }
     if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
     const float sg = 1.f / (1.f + expf(-alpha * g));
     st_f(out, out_dtype, i, g * sg * (u + up_shift));
   }
+}
+
+// out[n, :] = table[ids[n], :] * scale + pair[row(n), :], row = (prev * mul_prev + id * mul_cur) mod buckets, or row `buckets`
+// (the table's last) for a token without a predecessor (prev < 0): a hashed embedding of the (previous, current) pair
+__global__ void embed_bigram_kernel(float* out, const void* table, const void* pair, int t_dtype, const int* ids, const int* prev,
+                                    float scale, int width, int vocab, int buckets, int64_t mul_prev, int64_t mul_cur) {
+  const int row = blockIdx.x;
+  int id = ids[row];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const int pv = prev[row];
+  const int64_t pr = pv < 0 ? buckets : (int64_t) (((int64_t) pv * mul_prev + (int64_t) id * mul_cur) % buckets);
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    out[(int64_t) row * width + c] = fmaf(ld_f(table, t_dtype, (int64_t) id * width + c), scale, ld_f(pair, t_dtype, pr * width + c));
+}
+
+// Residual step of a sublayer between two layer norms and the next sublayer's input in one pass over the row:
+//   x <- x + out_scale * LN(y; w_post, b_post);   h = LN(x; w_pre, b_pre)   (skipped when w_pre is NULL)
+// A thread re-reads only what it wrote itself, so the row needs no fence between the passes.
+__global__ void __launch_bounds__(256) residual_sandwich_layernorm_kernel(float* x, int64_t ldx, const float* y, int64_t ldy,
+                                                                          const void* w_post, const void* b_post, const void* w_pre,
+                                                                          const void* b_pre, int w_dtype, float eps, float out_scale,
+                                                                          void* h, int h_dtype, int64_t ldh, int cols) {
+  __shared__ float red[8];
+  __shared__ float bc;
+  const int row = blockIdx.x;
+  float* xr = x + (int64_t) row * ldx;
+  const float* yr = y + (int64_t) row * ldy;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 256) s += yr[c];
+  const float mean_y = block_sum_256(s, red, &bc) / (float) cols;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 256) { const float d = yr[c] - mean_y; ss = fmaf(d, d, ss); }
+  const float inv_y = 1.f / sqrtf(block_sum_256(ss, red, &bc) / (float) cols + eps);
+  s = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 256) {
+    float v = (yr[c] - mean_y) * inv_y * ld_f(w_post, w_dtype, c);
+    if (b_post) v += ld_f(b_post, w_dtype, c);
+    v = fmaf(out_scale, v, xr[c]);
+    xr[c] = v;
+    s += v;
+  }
+  if (!w_pre) return;
+  const float mean = block_sum_256(s, red, &bc) / (float) cols;
+  ss = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 256) { const float d = xr[c] - mean; ss = fmaf(d, d, ss); }
+  const float inv = 1.f / sqrtf(block_sum_256(ss, red, &bc) / (float) cols + eps);
+  for (int c = threadIdx.x; c < cols; c += 256) {
+    float v = (xr[c] - mean) * inv * ld_f(w_pre, w_dtype, c);
+    if (b_pre) v += ld_f(b_pre, w_dtype, c);
+    st_f(h, h_dtype, (int64_t) row * ldh + c, v);
+  }
+}
+
+// Per-layer token input (one CTA per row): e = the `sd` columns from e_off of side_embed[token]; g = gelu_tanh(W_gate x) * e;
+// y = W_proj g; x <- x + y / rms(y) * norm_w; then, when w_pre is given, h = LN(x; w_pre, b_pre) or the RMS norm (b_pre NULL and
+// pre_rms) of the NEXT layer.  Operands of the two products are rounded to the storage type (w_dtype) as a projection kernel
+// would; sums, the norm and the residual are fp32.  Shared memory: x row [width] | g [sd] | y [width].
+struct SideArgs {
+  float* x; int64_t ldx;
+  const void* side_embed; int64_t lde; int e_off;
+  const int* ids; int vocab;
+  const void *w_gate, *w_proj, *norm_w;
+  int w_dtype; float eps; int width, sd;
+  const void *w_pre, *b_pre; int pre_rms; void* h; int h_dtype; int64_t ldh;
+};
+__device__ __forceinline__ float round_like(float v, int dtype) {
+  return dtype == TB_DT_BF16 ? __bfloat162float(__float2bfloat16_rn(v)) : v;
+}
+__global__ void __launch_bounds__(256) token_side_input_kernel(SideArgs a) {
+  extern __shared__ float sm[];
+  __shared__ float red[8];
+  __shared__ float bc;
+  float* xs = sm;
+  float* gs = xs + a.width;
+  float* ys = gs + a.sd;
+  const int row = blockIdx.x, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  float* xr = a.x + (int64_t) row * a.ldx;
+  for (int c = threadIdx.x; c < a.width; c += 256) xs[c] = round_like(xr[c], a.w_dtype);
+  __syncthreads();
+  int id = a.ids[row];
+  id = id < 0 ? 0 : (id >= a.vocab ? a.vocab - 1 : id);
+  for (int j = warp; j < a.sd; j += 8) {
+    float acc = 0.f;
+    for (int c = lane; c < a.width; c += 32) acc = fmaf(ld_f(a.w_gate, a.w_dtype, (int64_t) j * a.width + c), xs[c], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) gs[j] = round_like(gelu_tanh_f(acc) * ld_f(a.side_embed, a.w_dtype, (int64_t) id * a.lde + a.e_off + j), a.w_dtype);
+  }
+  __syncthreads();
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < a.width; c += 256) {
+    float acc = 0.f;
+    for (int j = 0; j < a.sd; ++j) acc = fmaf(ld_f(a.w_proj, a.w_dtype, (int64_t) c * a.sd + j), gs[j], acc);
+    ys[c] = acc;
+    ss = fmaf(acc, acc, ss);
+  }
+  const float inv_y = 1.f / sqrtf(block_sum_256(ss, red, &bc) / (float) a.width + a.eps);
+  float s = 0.f, s2 = 0.f;
+  for (int c = threadIdx.x; c < a.width; c += 256) {
+    const float v = fmaf(ys[c] * inv_y, ld_f(a.norm_w, a.w_dtype, c), xr[c]);
+    xr[c] = v;
+    ys[c] = v;
+    s += v;
+    s2 = fmaf(v, v, s2);
+  }
+  if (!a.w_pre) return;
+  if (a.pre_rms) {
+    const float inv = 1.f / sqrtf(block_sum_256(s2, red, &bc) / (float) a.width + a.eps);
+    for (int c = threadIdx.x; c < a.width; c += 256) st_f(a.h, a.h_dtype, (int64_t) row * a.ldh + c, ys[c] * inv * ld_f(a.w_pre, a.w_dtype, c));
+    return;
+  }
+  const float mean = block_sum_256(s, red, &bc) / (float) a.width;
+  ss = 0.f;
+  for (int c = threadIdx.x; c < a.width; c += 256) { const float d = ys[c] - mean; ss = fmaf(d, d, ss); }
+  const float inv = 1.f / sqrtf(block_sum_256(ss, red, &bc) / (float) a.width + a.eps);
+  for (int c = threadIdx.x; c < a.width; c += 256) {
+    float v = (ys[c] - mean) * inv * ld_f(a.w_pre, a.w_dtype, c);
+    if (a.b_pre) v += ld_f(a.b_pre, a.w_dtype, c);
+    st_f(a.h, a.h_dtype, (int64_t) row * a.ldh + c, v);
+  }
+}
+
+// out = out_scale * (a / rms(a) * wa + b / rms(b) * wb): two streams side by side, each RMS-normalised with its own weight
+__global__ void __launch_bounds__(256) rmsnorm_pair_sum_kernel(float* out, int64_t ldo, const float* a, int64_t lda, const float* b,
+                                                               int64_t ldb, const void* wa, const void* wb, int w_dtype, float eps,
+                                                               float out_scale, int cols) {
+  __shared__ float red[8];
+  __shared__ float bc;
+  const int row = blockIdx.x;
+  const float* ar = a + (int64_t) row * lda;
+  const float* br = b + (int64_t) row * ldb;
+  float sa = 0.f, sb = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 256) { sa = fmaf(ar[c], ar[c], sa); sb = fmaf(br[c], br[c], sb); }
+  const float ia = 1.f / sqrtf(block_sum_256(sa, red, &bc) / (float) cols + eps);
+  const float ib = 1.f / sqrtf(block_sum_256(sb, red, &bc) / (float) cols + eps);
+  for (int c = threadIdx.x; c < cols; c += 256)
+    out[(int64_t) row * ldo + c] = out_scale * (ar[c] * ia * ld_f(wa, w_dtype, c) + br[c] * ib * ld_f(wb, w_dtype, c));
 }
 
 // fp32 rows (row stride ld) -> contiguous bf16: the residual stream as the operand of a tcgen05 projection
@@ -322,13 +471,72 @@ extern "C" int tb_concat_rows(void* out, int out_dtype, const float* a, int64_t 
   return 0;
 }
 
-extern "C" int tb_gated_act(void* out, int out_dtype, const float* gu, int rows, int ff, float alpha, float limit,
-                            float up_shift, tb_stream_t stream) {
-  if (!out || !gu || !dt_ok(out_dtype) || ff <= 0 || rows < 0) return -1;
+extern "C" int tb_gated_act(void* out, int out_dtype, const float* gu, int rows, int ff, int gate, float alpha, float limit,
+                            float up_shift, const float* row_scale, const int* row_index, tb_stream_t stream) {
+  if (!out || !gu || !dt_ok(out_dtype) || ff <= 0 || rows < 0 || (gate != TB_GATE_SIGMOID && gate != TB_GATE_GELU_TANH)) return -1;
+  if (row_index && !row_scale) return -1;
   if (rows == 0) return 0;
   const int64_t n = (int64_t) rows * ff;
   const int grid = (int) ((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-  gated_act_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(out, out_dtype, gu, n, ff, alpha, limit, up_shift);
+  gated_act_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(out, out_dtype, gu, n, ff, gate, alpha, limit, up_shift, row_scale, row_index);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_embed_bigram(float* out, const void* table, const void* pair, int t_dtype, const int* ids, const int* prev_ids,
+                               float scale, int rows, int width, int vocab, int buckets, int mul_prev, int mul_cur,
+                               tb_stream_t stream) {
+  if (!out || !table || !pair || !ids || !prev_ids || !dt_ok(t_dtype) || width <= 0 || vocab <= 0 || buckets <= 0 || rows < 0 ||
+      mul_prev < 0 || mul_cur < 0)
+    return -1;
+  if (rows == 0) return 0;
+  embed_bigram_kernel<<<rows, 128, 0, (cudaStream_t) stream>>>(out, table, pair, t_dtype, ids, prev_ids, scale, width, vocab, buckets,
+                                                               mul_prev, mul_cur);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_residual_sandwich_layernorm_rows(float* x, int64_t ldx, const float* y, int64_t ldy, const void* w_post,
+                                                   const void* b_post, const void* w_pre, const void* b_pre, int w_dtype, float eps,
+                                                   float out_scale, void* h, int h_dtype, int64_t ldh, int rows, int cols,
+                                                   tb_stream_t stream) {
+  if (!x || !y || !w_post || !dt_ok(w_dtype) || cols <= 0 || rows < 0) return -1;
+  if (w_pre && (!h || !dt_ok(h_dtype))) return -1;
+  if (rows == 0) return 0;
+  residual_sandwich_layernorm_kernel<<<rows, 256, 0, (cudaStream_t) stream>>>(x, ldx, y, ldy, w_post, b_post, w_pre, b_pre, w_dtype,
+                                                                              eps, out_scale, h, h_dtype, ldh, cols);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_token_side_input(float* x, int64_t ldx, const void* side_embed, int64_t lde, int e_off, const int* ids, int vocab,
+                                   const void* w_gate, const void* w_proj, const void* norm_w, int w_dtype, float eps, int rows,
+                                   int width, int sd, const void* w_pre, const void* b_pre, int pre_rms, void* h, int h_dtype,
+                                   int64_t ldh, tb_stream_t stream) {
+  if (!x || !side_embed || !ids || !w_gate || !w_proj || !norm_w || !dt_ok(w_dtype) || width <= 0 || sd <= 0 || rows < 0 ||
+      vocab <= 0 || e_off < 0)
+    return -1;
+  if (w_pre && (!h || !dt_ok(h_dtype))) return -1;
+  const size_t smem = ((size_t) 2 * width + sd) * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  if (rows == 0) return 0;
+  static size_t raised = 48 * 1024;
+  if (smem > raised) {
+    TB_CHECK_CUDA(cudaFuncSetAttribute(token_side_input_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    raised = smem;
+  }
+  SideArgs a{x, ldx, side_embed, lde, e_off, ids, vocab, w_gate, w_proj, norm_w, w_dtype, eps, width, sd, w_pre, b_pre, pre_rms, h,
+             h_dtype, ldh};
+  token_side_input_kernel<<<rows, 256, smem, (cudaStream_t) stream>>>(a);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_rmsnorm_pair_sum(float* out, int64_t ldo, const float* a, int64_t lda, const float* b, int64_t ldb, const void* wa,
+                                   const void* wb, int w_dtype, float eps, float out_scale, int rows, int cols, tb_stream_t stream) {
+  if (!out || !a || !b || !wa || !wb || !dt_ok(w_dtype) || cols <= 0 || rows < 0) return -1;
+  if (rows == 0) return 0;
+  rmsnorm_pair_sum_kernel<<<rows, 256, 0, (cudaStream_t) stream>>>(out, ldo, a, lda, b, ldb, wa, wb, w_dtype, eps, out_scale, cols);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

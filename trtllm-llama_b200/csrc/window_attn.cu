@@ -113,6 +113,85 @@ __global__ void __launch_bounds__(256) qkv_conv_rope_append_kernel(T* q_out, T* 
   }
 }
 
+
+// The same step for an attention whose queries and keys are RMS-normalised over the WHOLE projection (all heads at once, one
+// weight per channel) between the convolution and the rotation, and whose values may be the keys themselves as they leave the
+// convolution (before norm and rotation): proj holds q (H dim) | k (G dim) [| v (G vdim) when the values are projected].
+// One CTA per row: pass 1 convolves every channel into shared memory and sums the squares of the q part and of the k part,
+// pass 2 normalises, rotates pairs and stores.  Shared memory: the row's C convolved channels (fp32).
+struct QkNormArgs {
+  QkvArgs a;
+  const void *norm_q, *norm_k;               // [H dim], [G dim] in w_dtype, or NULL
+  float eps;
+  int tied;                                  // values = convolved keys (vdim == dim, no v columns in proj)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) qk_conv_norm_rope_append_kernel(T* q_out, T* pool, QkNormArgs n) {
+  extern __shared__ float ys[];
+  __shared__ float red[2][8];
+  __shared__ float inv_s[2];
+  const QkvArgs& a = n.a;
+  const int Cq = a.H * a.dim, Ck = a.G * a.dim, Cv = a.G * a.vdim, C = Cq + Ck + (n.tied ? 0 : Cv);
+  const int row = blockIdx.x;
+  const int e = a.tok_seq[row], pos = a.tok_pos[row], past = a.seq_past[e], start = a.seq_start[e];
+  const float* st = a.taps > 1 ? a.state + (int64_t) a.seq_slot[e] * (a.taps - 1) * C : nullptr;
+  const int64_t slot = (int64_t) a.block_table[(int64_t) e * a.max_blocks + pos / a.page] * a.page + pos % a.page;
+  T* q_row = q_out + (int64_t) row * Cq;
+  T* kv_row = pool + slot * (Ck + Cv);
+  const bool carry = a.state_rw && a.taps > 1 && a.seq_len[e] == 1;
+  float* st_rw = carry ? a.state_rw + (int64_t) a.seq_slot[e] * (a.taps - 1) * C : nullptr;
+  float sq = 0.f, sk = 0.f;
+  for (int ch = threadIdx.x; ch < C; ch += 256) {
+    const float y = a.conv_w ? conv_at(a, st, C, ch, pos, past, start) : a.proj[(int64_t) row * a.ldp + ch];
+    ys[ch] = y;
+    if (ch < Cq) sq = fmaf(y, y, sq); else if (ch < Cq + Ck) sk = fmaf(y, y, sk);
+    if (carry) {
+      const int m = a.taps - 1;
+      for (int j = 0; j + 1 < m; ++j) st_rw[(int64_t) j * C + ch] = pos - m + 1 + j >= 0 ? st_rw[(int64_t) (j + 1) * C + ch] : 0.f;
+      st_rw[(int64_t) (m - 1) * C + ch] = a.proj[(int64_t) row * a.ldp + ch];
+    }
+  }
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  if (threadIdx.x % 32 == 0) { red[0][threadIdx.x / 32] = sq; red[1][threadIdx.x / 32] = sk; }
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    const int w = threadIdx.x / 32, l = threadIdx.x % 32;
+    float v = l < 8 ? red[w][l] : 0.f;
+    v = warp_sum(v);
+    if (l == 0) inv_s[w] = 1.f / sqrtf(v / (float) (w == 0 ? Cq : Ck) + n.eps);
+  }
+  __syncthreads();
+  const bool normed = n.norm_q != nullptr;
+  const float iq = normed ? inv_s[0] : 1.f, ik = normed ? inv_s[1] : 1.f;
+  const float* cs_row = a.dims > 0 ? a.table + (int64_t) row * a.dims : nullptr;      // [dims / 2][cos, sin]
+  // pairs of neighbouring channels of q | k: norm, weight, rotation, store (dim is even whenever anything is rotated)
+  for (int ch = 2 * threadIdx.x; ch < Cq + Ck; ch += 512) {
+    const bool two = ch + 1 < Cq + Ck;
+    const bool isq = ch < Cq;
+    const int c0 = isq ? ch : ch - Cq;
+    float y0 = ys[ch] * (isq ? iq : ik), y1 = two ? ys[ch + 1] * (ch + 1 < Cq ? iq : ik) : 0.f;
+    if (normed) {
+      y0 *= ld_w(isq ? n.norm_q : n.norm_k, a.w_dtype, c0);
+      if (two) y1 *= (ch + 1 < Cq) ? ld_w(n.norm_q, a.w_dtype, ch + 1) : ld_w(n.norm_k, a.w_dtype, ch + 1 - Cq);
+    }
+    const int d = c0 % a.dim;
+    if (d < a.dims) {
+      const float c = cs_row[d], sn = cs_row[d + 1];
+      const float u = y0, v = y1;
+      y0 = fmaf(u, c, -v * sn);
+      y1 = fmaf(v, c, u * sn);
+    }
+    if (isq) q_row[ch] = from_f<T>(y0); else kv_row[ch - Cq] = from_f<T>(y0);
+    if (two) {
+      if (ch + 1 < Cq) q_row[ch + 1] = from_f<T>(y1); else kv_row[ch + 1 - Cq] = from_f<T>(y1);
+    }
+  }
+  // values: the convolved keys as they are, or the convolved value channels
+  for (int c = threadIdx.x; c < Cv; c += 256) kv_row[Ck + c] = from_f<T>(ys[n.tied ? Cq + c : Cq + Ck + c]);
+}
+
 constexpr int kWarps = 4;
 constexpr int kTile = 32;
 constexpr int kMaxVPerLane = 16;         // vdim <= 512
@@ -125,6 +204,7 @@ struct AttnArgs {
   float scale;
   int vsh, GV;                             // key heads per value head (key head g reads value head g / vsh), GV = G / vsh value heads
   int out_f32;                             // the result is stored as fp32 whatever the storage type
+  int keep;                                // with a window: positions below `keep` stay visible to every later row
 };
 
 // shared memory (fp32): keys [32][dim + 1] | values [32][vdim] | per warp q [dim]
@@ -152,18 +232,23 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(T* out, c
   for (int c = 0; c < kMaxVPerLane; ++c) acc[c] = 0.f;
   float m = -INFINITY, l = 0.f;
   if (a.sink) { m = ld_w(a.sink, a.sink_dtype, head); l = 1.f; }
-  for (int j0 = (lo / kTile) * kTile; j0 <= pos; j0 += kTile) {
+  // kept first positions below the window: their blocks come first, then the window's blocks (an order fixed by pos alone)
+  const int keep_lo = a.keep < lo ? a.keep : lo;                       // kept positions that the window does not cover
+  const int kept_blocks = min((keep_lo + kTile - 1) / kTile, lo / kTile);
+  const int first_block = lo / kTile - kept_blocks;
+  for (int jb = first_block; jb * kTile <= pos; ++jb) {
+    const int j0 = (jb < lo / kTile ? jb - first_block : jb) * kTile;
     __syncthreads();
     for (int e = threadIdx.x; e < kTile * a.dim; e += kWarps * 32) {
       const int jj = e / a.dim, d = e % a.dim, j = j0 + jj;
       float v = 0.f;
-      if (j >= lo && j <= pos) v = to_f<T>(pool[((int64_t) bt[j / a.page] * a.page + j % a.page) * E + g * a.dim + d]);
+      if ((j >= lo || j < a.keep) && j <= pos) v = to_f<T>(pool[((int64_t) bt[j / a.page] * a.page + j % a.page) * E + g * a.dim + d]);
       keys[jj * LDK + d] = v;
     }
     for (int e = threadIdx.x; e < kTile * a.vdim; e += kWarps * 32) {
       const int jj = e / a.vdim, d = e % a.vdim, j = j0 + jj;
       float v = 0.f;
-      if (j >= lo && j <= pos)
+      if ((j >= lo || j < a.keep) && j <= pos)
         v = to_f<T>(pool[((int64_t) bt[j / a.page] * a.page + j % a.page) * E + a.G * a.dim + (g / a.vsh) * a.vdim + d]);
       vals[jj * a.vdim + d] = v;
     }
@@ -172,7 +257,7 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(T* out, c
     float s = 0.f;
     const float* kr = keys + lane * LDK;
     for (int d = 0; d < a.dim; ++d) s = fmaf(qs[d], kr[d], s);
-    const bool vis = j0 + lane >= lo && j0 + lane <= pos;
+    const bool vis = (j0 + lane >= lo || j0 + lane < a.keep) && j0 + lane <= pos;
     s = vis ? s : -INFINITY;
     const float m_new = fmaxf(m, warp_max(s));          // finite: every visited block holds a visible key
     const float p = vis ? expf(s - m_new) : 0.f;
@@ -299,7 +384,7 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
   auto locate_tile = [&](int kt, int stage) {
     if (threadIdx.x < kMmaKeys) {
       const int j = kt * kMmaKeys + threadIdx.x;
-      key_row[stage][threadIdx.x] = (j >= lo_cta && j <= p_last) ? ((int64_t) bt[j / a.page] * a.page + j % a.page) * E : -1;
+      key_row[stage][threadIdx.x] = ((j >= lo_cta || j < a.keep) && j <= p_last) ? ((int64_t) bt[j / a.page] * a.page + j % a.page) * E : -1;
     }
   };
   auto load_tile = [&](int stage) {
@@ -316,8 +401,15 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
       cp_async16(vd + jj * LDV + c, r >= 0 ? pool + r + a.G * DIM + (g / a.vsh) * VDIM + c : pool, r >= 0);
     }
   };
-  const int kt0 = lo_cta / kMmaKeys + split, kt1 = p_last / kMmaKeys;
-  locate_tile(kt0, 0);
+  // the CTA's key tiles in visiting order: those of kept first positions that lie below the window's first tile, then the
+  // window's tiles; index i of that list is tile (i < n_kept ? i : wt0 + i - n_kept)
+  const int wt0 = lo_cta / kMmaKeys;
+  const int keep_lo = a.keep < lo_cta ? a.keep : lo_cta;
+  const int n_kept = min((keep_lo + kMmaKeys - 1) / kMmaKeys, wt0);
+  const int n_tiles = n_kept + p_last / kMmaKeys - wt0 + 1;
+  auto tile_at = [&](int i) { return i < n_kept ? i : wt0 + i - n_kept; };
+  const int kt0 = split, kt1 = n_tiles - 1;              // indices into the list from here on
+  locate_tile(tile_at(kt0 < n_tiles ? kt0 : 0), 0);
 
   // the two rows of this thread: warp * 16 + gq and + 8
   int pos_r[2], lo_r[2], head_r[2];
@@ -349,7 +441,7 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
 #pragma unroll
   for (int kk = 0; kk < DIM / 16; ++kk)
     ldsm_x4(qf[kk], qs + (warp * 16 + lane % 16) * LDQ + kk * 16 + (lane / 16) * 8);
-  if (kt0 + nsplit <= kt1) locate_tile(kt0 + nsplit, 1);   // visible behind the loop's first barrier, like the end of the
+  if (kt0 + nsplit <= kt1) locate_tile(tile_at(kt0 + nsplit), 1);   // visible behind the loop's first barrier, like the end of the
                                                            // fragment loads from the stage the query tile borrows
   int stage = 0;
   for (int kt = kt0; kt <= kt1; kt += nsplit, stage ^= 1) {
@@ -358,10 +450,10 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
     cp_async_wait<0>();
     __syncthreads();
     if (kt + nsplit <= kt1) { load_tile(stage ^ 1); cp_async_commit(); }
-    if (kt + 2 * nsplit <= kt1) locate_tile(kt + 2 * nsplit, stage);   // read by load_tile behind the next barrier
+    if (kt + 2 * nsplit <= kt1) locate_tile(tile_at(kt + 2 * nsplit), stage);   // read by load_tile behind the next barrier
     const __nv_bfloat16* kd = ks + stage * kMmaKeys * LDQ;
     const __nv_bfloat16* vd = vs + stage * kMmaKeys * LDV;
-    const int j0 = kt * kMmaKeys;
+    const int j0 = tile_at(kt) * kMmaKeys;
     float s[8][4];
 #pragma unroll
     for (int n = 0; n < 8; ++n)
@@ -384,7 +476,7 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int h = c >> 1, j = j0 + n * 8 + 2 * tq + (c & 1);
-        const float v = (j >= lo_r[h] && j <= pos_r[h]) ? s[n][c] * scale2 : -INFINITY;
+        const float v = ((j >= lo_r[h] || j < a.keep) && j <= pos_r[h]) ? s[n][c] * scale2 : -INFINITY;
         s[n][c] = v;
         mx[h] = fmaxf(mx[h], v);
       }
@@ -557,6 +649,44 @@ extern "C" int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const
   return 0;
 }
 
+extern "C" int tb_qk_conv_norm_rope_append(void* q_out, void* pool, int dtype, const float* proj, int64_t ldp, const void* conv_w,
+                                           const void* norm_q, const void* norm_k, int w_dtype, float eps, const float* state,
+                                           const float* table, int dims, const int* tok_seq, const int* tok_pos, const int* seq_start,
+                                           const int* seq_past, const int* seq_slot, const int* block_table, int max_blocks, int page,
+                                           int rows, int heads, int kv_heads, int dim, int vdim, int taps, int tied_values,
+                                           float* state_rw, const int* seq_len, tb_stream_t stream) {
+  if (!q_out || !pool || !proj || !tok_seq || !tok_pos || !seq_start || !seq_past || !seq_slot || !block_table) return -1;
+  if ((dtype != TB_DT_F32 && dtype != TB_DT_BF16) || (w_dtype != TB_DT_F32 && w_dtype != TB_DT_BF16)) return -1;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 || taps < 1 || taps > kMaxTaps || page <= 0 ||
+      rows < 0 || dims < 0 || dims % 2 || dims > dim || (dims > 0 && (dim % 2 || !table)) || (taps > 1 && (!state || !conv_w)) ||
+      (tied_values && vdim != dim) || (!norm_q != !norm_k))
+    return -1;
+  if (rows == 0) return 0;
+  if (state_rw && (state_rw != state || !seq_len)) return -1;
+  const int C = (heads + kv_heads) * dim + (tied_values ? 0 : kv_heads * vdim);
+  const size_t smem = (size_t) C * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  QkNormArgs n{{proj, ldp, conv_w, w_dtype, state, table, tok_seq, tok_pos, seq_start, seq_past, seq_slot, block_table, max_blocks,
+                page, rows, heads, kv_heads, dim, vdim, dims, taps, state_rw, seq_len},
+               norm_q, norm_k, eps, tied_values ? 1 : 0};
+  static size_t raised_f = 48 * 1024, raised_b = 48 * 1024;
+  if (dtype == TB_DT_F32) {
+    if (smem > raised_f) {
+      TB_CHECK_CUDA(cudaFuncSetAttribute(qk_conv_norm_rope_append_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+      raised_f = smem;
+    }
+    qk_conv_norm_rope_append_kernel<float><<<rows, 256, smem, (cudaStream_t) stream>>>((float*) q_out, (float*) pool, n);
+  } else {
+    if (smem > raised_b) {
+      TB_CHECK_CUDA(cudaFuncSetAttribute(qk_conv_norm_rope_append_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+      raised_b = smem;
+    }
+    qk_conv_norm_rope_append_kernel<__nv_bfloat16><<<rows, 256, smem, (cudaStream_t) stream>>>((__nv_bfloat16*) q_out, (__nv_bfloat16*) pool, n);
+  }
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 extern "C" int tb_window_attention_tensor_cores(int dtype, int heads, int kv_heads, int dim, int vdim) {
   if (dtype != TB_DT_BF16 || heads <= 0 || kv_heads <= 0 || heads % kv_heads) return 0;
 #define X(D, V) if (dim == D && vdim == V) return 1;
@@ -573,7 +703,7 @@ extern "C" int tb_window_attention(void* out, const void* q, const void* pool, i
                                    tb_stream_t stream) {
   return tb_window_attention_shared_values(out, 0, q, pool, dtype, gate, ldg, sink, sink_dtype, tok_seq, tok_pos, block_table,
                                            seq_start, seq_len, seq_past, seqs, max_len, max_blocks, page, rows, heads, kv_heads, 1,
-                                           dim, vdim, scale, window, mode, nsplit, workspace, stream);
+                                           dim, vdim, scale, window, 0, mode, nsplit, workspace, stream);
 }
 
 extern "C" int tb_window_attention_shared_values(void* out, int out_f32, const void* q, const void* pool, int dtype,
@@ -581,9 +711,9 @@ extern "C" int tb_window_attention_shared_values(void* out, int out_f32, const v
                                                  const int* tok_seq, const int* tok_pos, const int* block_table,
                                                  const int* seq_start, const int* seq_len, const int* seq_past, int seqs,
                                                  int max_len, int max_blocks, int page, int rows, int heads, int kv_heads,
-                                                 int v_share, int dim, int vdim, float scale, int window, int mode, int nsplit,
-                                                 float* workspace, tb_stream_t stream) {
-  if (!out || !q || !pool || !tok_seq || !tok_pos || !block_table) return -1;
+                                                 int v_share, int dim, int vdim, float scale, int window, int keep_first, int mode,
+                                                 int nsplit, float* workspace, tb_stream_t stream) {
+  if (!out || !q || !pool || !tok_seq || !tok_pos || !block_table || keep_first < 0) return -1;
   if (v_share <= 0 || kv_heads % v_share) return -1;
   if (dtype != TB_DT_F32 && dtype != TB_DT_BF16) return -1;
   if (sink && sink_dtype != TB_DT_F32 && sink_dtype != TB_DT_BF16) return -1;
@@ -592,7 +722,7 @@ extern "C" int tb_window_attention_shared_values(void* out, int out_f32, const v
     return -1;
   if (rows == 0) return 0;
   AttnArgs a{gate, ldg, sink, sink_dtype, tok_seq, tok_pos, block_table, max_blocks, page, heads, kv_heads, dim, vdim,
-             window, scale, v_share, kv_heads / v_share, out_f32 ? 1 : 0};
+             window, scale, v_share, kv_heads / v_share, out_f32 ? 1 : 0, window > 0 ? keep_first : 0};
   cudaStream_t s = (cudaStream_t) stream;
   if (mode == 0 && seq_start && seq_len && seq_past && seqs > 0 && max_len > 0 && seqs <= 65535 &&
       tb_window_attention_tensor_cores(dtype, heads, kv_heads, dim, vdim) && (uintptr_t) q % 16 == 0 && (uintptr_t) pool % 16 == 0) {

@@ -46,8 +46,8 @@ class RaggedBatch:
     """Device-side description of one step (see include/trtllm_b200_ragged.h), uploaded as ONE int32 buffer."""
 
     def __init__(self, entries, want_rows, device, max_blocks=None):
-        """entries: [(token ids, past length, state slot, block ids)]; want_rows: row indices whose logits are wanted.
-        ``max_blocks`` pads the block table's row length (a replayed step graph needs it fixed)."""
+        """entries: [(token ids, past length, state slot, block ids[, the token before these, -1 for none])]; want_rows: row
+        indices whose logits are wanted.  ``max_blocks`` pads the block table's row length (a replayed step graph needs it fixed)."""
         self.device = device
         self.max_blocks = max(1, max(len(e[3]) for e in entries), max_blocks or 0)
         host = self._pack(entries, want_rows)
@@ -57,8 +57,12 @@ class RaggedBatch:
         self._views()
 
     def _pack(self, entries, want_rows):
-        tok_ids, tok_seq, tok_pos, start, length, past, slot, table = [], [], [], [], [], [], [], []
-        for i, (toks, p, s, blocks) in enumerate(entries):
+        tok_ids, tok_seq, tok_pos, tok_prev, start, length, past, slot, table = [], [], [], [], [], [], [], [], []
+        for i, entry in enumerate(entries):
+            toks, p, s, blocks = entry[:4]
+            toks = list(toks)
+            before = int(entry[4]) if len(entry) > 4 and entry[4] is not None else -1
+            tok_prev += [before if p > 0 else -1] + toks[:-1]
             start.append(len(tok_ids))
             length.append(len(toks))
             past.append(p)
@@ -70,15 +74,17 @@ class RaggedBatch:
         self.num_rows, self.num_seqs, self.num_want = len(tok_ids), len(entries), len(want_rows)
         self.max_len = max(length)        # host-side hints for kernels that size their grids by the longest portion
         self.max_pos = max(tok_pos)       # ... and by context length
-        self._sizes = [len(tok_ids)] * 3 + [len(entries)] * 4 + [len(table), len(want_rows)]
-        return torch.tensor(tok_ids + tok_seq + tok_pos + start + length + past + slot + table + list(want_rows), dtype=torch.int32)
+        self._sizes = [len(tok_ids)] * 4 + [len(entries)] * 4 + [len(table), len(want_rows)]
+        return torch.tensor(tok_ids + tok_seq + tok_pos + tok_prev + start + length + past + slot + table + list(want_rows),
+                            dtype=torch.int32)
 
     def _views(self):
         off, views = 0, []
         for n in self._sizes:
             views.append(self._dev[off:off + n])
             off += n
-        (self.tok_ids, self.tok_seq, self.tok_pos, self.seq_start, self.seq_len, self.seq_past, self.seq_slot,
+        # tok_prev: the token before each row in its sequence (-1 at position 0) — part of a sequence's state between steps
+        (self.tok_ids, self.tok_seq, self.tok_pos, self.tok_prev, self.seq_start, self.seq_len, self.seq_past, self.seq_slot,
          self.block_table, self.want_rows) = views
 
     def refill(self, entries, want_rows):
@@ -111,6 +117,7 @@ class _Live:
     handle: GenerationSequence
     slot: int
     length: int = 0
+    last_token: int = -1               # the newest token it holds (models whose embedding reads the previous token)
 
 
 class InflightSession:
@@ -167,7 +174,7 @@ class InflightSession:
                     s = self._admit(seq_id)
                     fresh.append(seq_id)
                 self.kv_cache_manager.reserve(s.handle, s.length + len(tokens))
-                rows.append((tokens, s.length, s.slot, self.kv_cache_manager.blocks_of(s.handle)))
+                rows.append((tokens, s.length, s.slot, self.kv_cache_manager.blocks_of(s.handle), s.last_token))
                 want_rows += [n + int(w) for w in want]
                 n += len(tokens)
         except Exception:
@@ -185,6 +192,7 @@ class InflightSession:
             logits = self.model.logits(x, batch.want_rows) if want_rows else None
         for seq_id, tokens, _ in entries:
             self.live[seq_id].length += len(tokens)
+            self.live[seq_id].last_token = int(tokens[-1])
         return logits
 
     def _generation_step_graph(self, rows):

@@ -58,4 +58,4 @@ def _load_llama_engine(model_dir, config, dtype="float16", device="cuda", rank=0
     return mc, tensors
 
 
-from . import mimolix, nililix, zobasun  # noqa: E402,F401  (they register themselves)
+from . import duzizen, mimolix, nililix, zobasun  # noqa: E402,F401  (they register themselves)

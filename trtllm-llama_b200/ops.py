@@ -344,6 +344,8 @@ from ._lib import ragged_lib as _rl  # noqa: E402
 
 DT_F32, DT_BF16 = 1, 2
 ACT_NONE, ACT_GELU_TANH, ACT_RELU_SQUARED = 0, 1, 3
+GATE_SIGMOID, GATE_GELU_TANH = 0, 1        # gated activations of a (gate, up) pair (TB_GATE_*)
+ROPE_INTERLEAVED, ROPE_HALF = 0, 1         # which elements a rotation pairs (TB_ROPE_*)
 COMPUTE_AUTO, COMPUTE_FMA32 = 0, 1
 # rows from which a bf16 projection goes to the tcgen05 kernel; below, the streaming GEMV (<= 8 rows) or the warp-MMA tiles
 TC_MIN_ROWS = 17
@@ -423,6 +425,19 @@ def cast_rows_bf16(x):
     return out
 
 
+def embed_bigram(table, pair, ids, prev_ids, scale, mul_prev, mul_cur):
+    """table[ids] * scale + pair[(prev * mul_prev + id * mul_cur) mod buckets]; a token without a predecessor (prev < 0) reads
+    the last row of ``pair`` ([buckets + 1, width])."""
+    _chk_dev(table, pair, ids, prev_ids)
+    if pair.dtype != table.dtype or pair.shape[1] != table.shape[1] or not pair.is_contiguous():
+        raise ValueError("embed_bigram: the pair table has the embedding's type and width")
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
+    check(_rl.tb_embed_bigram(_p(out), _p(table), _p(pair), _dt(table), _p(ids), _p(prev_ids), float(scale), ids.numel(),
+                              table.shape[1], table.shape[0], pair.shape[0] - 1, int(mul_prev), int(mul_cur), _stream()),
+          "tb_embed_bigram")
+    return out
+
+
 def embed_scaled(table, ids, scale):
     _chk_dev(table, ids)
     out = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
@@ -448,8 +463,8 @@ def rmsnorm_rows(x, w, eps, w_offset=0.0, out=None, out_dtype=None, accumulate=F
     return out
 
 
-def linear_gated(a, w_gate_up, out_dtype, alpha, limit, up_shift):
-    """gate‖up projection and the clamped gated activation in one kernel when the step has few rows (streaming GEMV);
+def linear_gated(a, w_gate_up, out_dtype, alpha, limit, up_shift, gate=GATE_SIGMOID):
+    """gate‖up projection and the gated activation in one kernel when the step has few rows (streaming GEMV);
     returns None when the shape is not eligible — the caller then uses ``linear`` + ``gated_act``."""
     _chk_dev(a, w_gate_up)
     M, K, ff = a.shape[0], a.shape[1], w_gate_up.shape[0] // 2
@@ -457,19 +472,21 @@ def linear_gated(a, w_gate_up, out_dtype, alpha, limit, up_shift):
         return None
     out = torch.empty((M, ff), dtype=out_dtype, device=a.device)
     rc = _rl.tb_linear_gated(_p(out), _dt(out), out.stride(0), _p(a), _dt(a), a.stride(0), _p(w_gate_up), _dt(w_gate_up),
-                             M, ff, K, float(alpha), float(limit), float(up_shift), _stream())
+                             M, ff, K, int(gate), float(alpha), float(limit), float(up_shift), _stream())
     if rc == -3:
         return None
     check(rc, "tb_linear_gated")
     return out
 
 
-def gated_act(gu, out_dtype, alpha, limit, up_shift):
-    _chk_cuda(gu)
+def gated_act(gu, out_dtype, alpha, limit, up_shift, gate=GATE_SIGMOID, row_scale=None, row_index=None):
+    """Gated activation of fp32 [rows, 2 ff] (gate columns, then up columns).  ``row_scale`` (fp32): gate and up of row r are
+    first multiplied by row_scale[row_index[r]] (row_index int32, negative: 0) or row_scale[r]."""
+    _chk_cuda(gu, row_scale, row_index)
     rows, ff = gu.shape[0], gu.shape[1] // 2
     out = torch.empty((rows, ff), dtype=out_dtype, device=gu.device)
-    check(_rl.tb_gated_act(_p(out), _dt(out), _p(gu), rows, ff, float(alpha), float(limit), float(up_shift), _stream()),
-          "tb_gated_act")
+    check(_rl.tb_gated_act(_p(out), _dt(out), _p(gu), rows, ff, int(gate), float(alpha), float(limit), float(up_shift),
+                           _p(row_scale), _p(row_index), _stream()), "tb_gated_act")
     return out
 
 
@@ -593,11 +610,13 @@ def qkv_conv_rope_append(proj, conv_w, state, table, dims, pool, batch, page, he
     return q
 
 
-def window_attention(q, pool, batch, page, kv_heads, vdim, scale, window, sink=None, gate=None, v_share=1, out_f32=False):
+def window_attention(q, pool, batch, page, kv_heads, vdim, scale, window, sink=None, gate=None, v_share=1, out_f32=False,
+                     keep_first=0):
     """Grouped-query attention of every row over the last ``window`` cached positions of its sequence (0: all), with an
     optional softmax sink per head and an optional per-head sigmoid gate (fp32 logits [N, >= heads], any row stride).
     ``v_share`` > 1: neighbouring key heads share a value head (key head g reads value head g // v_share; the pool entry
-    holds kv_heads key heads and kv_heads // v_share value heads).  ``out_f32``: the result is fp32 in every storage mode."""
+    holds kv_heads key heads and kv_heads // v_share value heads).  ``out_f32``: the result is fp32 in every storage mode.
+    ``keep_first``: with a window, the first positions of a sequence that every later row still sees."""
     _chk_cuda(q, pool, sink)
     _chk_dev(gate)
     rows, heads, dim = q.shape
@@ -608,7 +627,7 @@ def window_attention(q, pool, batch, page, kv_heads, vdim, scale, window, sink=N
     if not FORCE_SIMT_ATTENTION and _rl.tb_window_attention_tensor_cores(_dt(pool), heads, kv_heads, dim, vdim):
         # few row blocks (generation steps): deal each block's key tiles to several CTAs so that the chip reads the cache
         ctas = -(-batch.max_len * (heads // kv_heads) // 64) * batch.num_seqs * kv_heads
-        span = min(window, batch.max_pos + 1) if window else batch.max_pos + 1
+        span = min(window + keep_first, batch.max_pos + 1) if window else batch.max_pos + 1
         nsplit = max(1, min(32, 296 // ctas, span // 64 + 1))
         if nsplit > 1:
             ws = torch.empty((rows * heads * nsplit * (vdim + 2),), dtype=torch.float32, device=q.device)
@@ -616,9 +635,41 @@ def window_attention(q, pool, batch, page, kv_heads, vdim, scale, window, sink=N
         _p(out), int(out_f32), _p(q), _p(pool), _dt(pool), _p(gate), gate.stride(0) if gate is not None else 0, _p(sink),
         _dt(sink) if sink is not None else 0, _p(batch.tok_seq), _p(batch.tok_pos), _p(batch.block_table), _p(batch.seq_start),
         _p(batch.seq_len), _p(batch.seq_past), batch.num_seqs, batch.max_len, batch.max_blocks, page, rows, heads, kv_heads,
-        int(v_share), dim, vdim, float(scale), int(window), 1 if FORCE_SIMT_ATTENTION else 0, nsplit, _p(ws), _stream()),
+        int(v_share), dim, vdim, float(scale), int(window), int(keep_first) if window else 0, 1 if FORCE_SIMT_ATTENTION else 0,
+        nsplit, _p(ws), _stream()),
         "tb_window_attention_shared_values")
     return out
+
+
+def qk_conv_norm_rope_append(proj, conv_w, norm_q, norm_k, eps, state, table, dims, pool, batch, page, heads, kv_heads, dim, vdim,
+                             tied_values):
+    """Projected rows (fp32 [N, >= C], q | k [| v]) -> short causal convolution (``conv_w`` None: none) -> RMS norm of the whole
+    q part and of the whole k part with a weight per channel (both None: none) -> rotation of q and k -> queries [N, heads, dim]
+    in the pool's type, keys and values into the pages (``tied_values``: the values are the convolved keys before norm and
+    rotation); then the carried inputs move on."""
+    _chk_dev(proj, conv_w, norm_q, norm_k, state, table, pool)
+    rows = proj.shape[0]
+    taps = conv_w.shape[1] if conv_w is not None else 1
+    C = (heads + kv_heads) * dim + (0 if tied_values else kv_heads * vdim)
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[1] < C:
+        raise ValueError("qk_conv_norm_rope_append: proj fp32 [N, >= C]")
+    if conv_w is not None and (tuple(conv_w.shape) != (C, taps) or not conv_w.is_contiguous()):
+        raise ValueError("qk_conv_norm_rope_append: conv_w [C, taps] contiguous")
+    if pool.shape[1] != kv_heads * (dim + vdim):
+        raise ValueError("qk_conv_norm_rope_append: pool entry != kv_heads * (dim + vdim)")
+    wt = conv_w if conv_w is not None else norm_q
+    q = torch.empty((rows, heads, dim), dtype=pool.dtype, device=proj.device)
+    st = _p(state) if taps > 1 else None
+    check(_rl.tb_qk_conv_norm_rope_append(
+        _p(q), _p(pool), _dt(pool), _p(proj), proj.stride(0), _p(conv_w), _p(norm_q), _p(norm_k), _dt(wt) if wt is not None else DT_F32,
+        float(eps), st, _p(table), int(dims), _p(batch.tok_seq), _p(batch.tok_pos), _p(batch.seq_start), _p(batch.seq_past),
+        _p(batch.seq_slot), _p(batch.block_table), batch.max_blocks, page, rows, heads, kv_heads, dim, vdim, taps, int(bool(tied_values)),
+        st, _p(batch.seq_len) if taps > 1 else None, _stream()), "tb_qk_conv_norm_rope_append")
+    if taps > 1 and batch.max_len > 1:       # sequences that bring one row were moved on by the kernel above
+        check(_rl.tb_causal_conv1d_update(_p(state), _p(proj), proj.stride(0), _p(batch.seq_start), _p(batch.seq_len),
+                                          _p(batch.seq_past), _p(batch.seq_slot), batch.num_seqs, C, taps, 1, _stream()),
+              "tb_causal_conv1d_update")
+    return q
 
 
 def qk_norm_append(proj, w_q, w_k, eps, pool, batch, page, q_vectors, k_vectors, dim, v_channels, temp_coef=0.0, temp_every=0):
@@ -699,6 +750,120 @@ def gated_rmsnorm_heads(o, w, eps, out_dtype, gate=None):
     out = torch.empty((rows, heads, vdim), dtype=out_dtype, device=o.device)
     check(_rl.tb_gated_rmsnorm_heads(_p(out), _dt(out), _p(o), _p(gate), gate.stride(0) if gate is not None else 0, _p(w),
                                      _dt(w) if w is not None else 0, float(eps), rows, heads, vdim, _stream()), "tb_gated_rmsnorm_heads")
+    return out
+
+
+def rope_heads(x, table, heads, dim, dims, layout, split=0, scale_lo=1.0, scale_hi=1.0, out=None):
+    """x fp32 [N, >= heads * dim] (any row stride) -> fp32 [N, heads * dim] with the first ``dims`` elements of every head rotated
+    (pairs by ``layout``: ROPE_INTERLEAVED / ROPE_HALF); heads below ``split`` are multiplied by scale_lo, the others by scale_hi."""
+    _chk_dev(x, table, out)
+    if x.dtype != torch.float32 or x.stride(1) != 1 or x.shape[1] < heads * dim:
+        raise ValueError("rope_heads: fp32 rows of at least heads * dim columns")
+    if out is None:
+        out = torch.empty((x.shape[0], heads * dim), dtype=torch.float32, device=x.device)
+    check(_rl.tb_rope_heads(_p(out), out.stride(0), _p(x), x.stride(0), _p(table), x.shape[0], heads, dim, int(dims), int(layout),
+                            int(split), float(scale_lo), float(scale_hi), _stream()), "tb_rope_heads")
+    return out
+
+
+def mlstm_gates(proj, col_i, col_f, bias_i, bias_f, cap, m_state, batch, heads):
+    """Exponential gates of a matrix memory from the projected logits (columns col_i.. / col_f.. of fp32 ``proj``): -> (log_ab fp32
+    [N, heads, 2] = ln decay, ln input weight; m fp32 [N, heads] the running maximum).  ``m_state``: fp32 view [slots, >= heads] of
+    the sequences' maxima (row stride = the slot stride), read and written."""
+    _chk_dev(proj, bias_i, bias_f, m_state)
+    rows = proj.shape[0]
+    log_ab = torch.empty((rows, heads, 2), dtype=torch.float32, device=proj.device)
+    m = torch.empty((rows, heads), dtype=torch.float32, device=proj.device)
+    b = bias_i if bias_i is not None else bias_f
+    check(_rl.tb_mlstm_gates(_p(log_ab), _p(m), _p(proj), proj.stride(0), int(col_i), int(col_f), _p(bias_i), _p(bias_f),
+                             _dt(b) if b is not None else 0, float(cap or 0.0), _p(m_state), m_state.stride(0), _p(batch.seq_start),
+                             _p(batch.seq_len), _p(batch.seq_past), _p(batch.seq_slot), batch.num_seqs, heads, _stream()),
+          "tb_mlstm_gates")
+    return log_ab, m
+
+
+FORCE_ROW_SCAN = False      # A/B: the decayed linear attention row by row also for prompt portions
+
+
+def decay_attention_scan(q, k, v, state, batch, heads, dim, vdim, log_ab=None, head_decay=None, ones_col=False):
+    """S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t per (sequence, head) over every sequence's rows, from and into ``state``
+    (fp32 view [slots, >= heads * vcols * dim], row stride = the slot stride).  q, k fp32 [N, >= heads * dim], v fp32 [N, >= heads *
+    vdim] (any row strides).  ``log_ab`` fp32 [N, heads, 2] (ln a, ln b) or ``head_decay`` fp32 [heads] (a fixed, b = 1).
+    ``ones_col``: a further value column of ones (vcols = vdim + 1).  -> fp32 [N, heads, vcols]."""
+    _chk_dev(q, k, v, state, log_ab, head_decay)
+    for t in (q, k, v):
+        if t.dtype != torch.float32 or t.stride(1) != 1:
+            raise ValueError("decay_attention_scan: fp32 rows with unit inner stride")
+    vcols = vdim + (1 if ones_col else 0)
+    out = torch.empty((q.shape[0], heads, vcols), dtype=torch.float32, device=q.device)
+    check(_rl.tb_decay_attention_scan(_p(out), _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(log_ab), _p(head_decay),
+                                      _p(state), state.stride(0), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
+                                      _p(batch.seq_slot), q.shape[0], batch.num_seqs, heads, dim, vdim, int(bool(ones_col)),
+                                      1 if FORCE_ROW_SCAN else batch.max_len, _stream()), "tb_decay_attention_scan")
+    return out
+
+
+def head_norm_gate(o, vdim, eps, out_dtype, w=None, w_per_head=False, gate=None, gate_act="silu", m=None, den_eps=1e-6):
+    """o fp32 [N, heads, vcols] -> [N, heads, vdim]: with ``m`` (fp32 [N, heads]) first o / (max(|o[..., vdim]|, exp(-m)) + den_eps);
+    then per head o / rms(o) * w * act(gate) (``w`` [vdim] or, ``w_per_head``, [heads * vdim]; gate fp32 logits [N, >= heads *
+    vdim], ``gate_act`` "silu" | "sigmoid")."""
+    _chk_dev(o, w, gate, m)
+    rows, heads, vcols = o.shape
+    if o.dtype != torch.float32 or not o.is_contiguous():
+        raise ValueError("head_norm_gate: o fp32 contiguous")
+    if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1):
+        raise ValueError("gate logits are fp32 with unit inner stride")
+    act = 0 if gate is None else {"silu": 1, "sigmoid": 2}[gate_act]
+    out = torch.empty((rows, heads, vdim), dtype=out_dtype, device=o.device)
+    check(_rl.tb_head_norm_gate(_p(out), _dt(out), _p(o), vcols, _p(m), float(den_eps), _p(gate), gate.stride(0) if gate is not None else 0,
+                                act, _p(w), _dt(w) if w is not None else 0, int(bool(w_per_head)), float(eps), rows, heads, vdim,
+                                _stream()), "tb_head_norm_gate")
+    return out
+
+
+def residual_sandwich_layernorm_rows(x, y, w_post, b_post, out_scale, eps, w_pre=None, b_pre=None, out_dtype=torch.float32):
+    """x += out_scale * layer_norm(y; w_post, b_post) in place; with ``w_pre`` also returns layer_norm(x; w_pre, b_pre) — the
+    residual step of a sublayer between two layer norms and the next sublayer's input in one kernel."""
+    _chk_dev(x, y, w_post, b_post, w_pre, b_pre)
+    if x.dtype != torch.float32 or y.dtype != torch.float32 or x.stride(1) != 1 or y.stride(1) != 1:
+        raise ValueError("residual_sandwich_layernorm_rows: fp32 rows")
+    h = torch.empty(x.shape, dtype=out_dtype, device=x.device) if w_pre is not None else None
+    check(_rl.tb_residual_sandwich_layernorm_rows(_p(x), x.stride(0), _p(y), y.stride(0), _p(w_post), _p(b_post), _p(w_pre), _p(b_pre),
+                                                  _dt(w_post), float(eps), float(out_scale), _p(h), _dt(h) if h is not None else 0,
+                                                  h.stride(0) if h is not None else 0, x.shape[0], x.shape[1], _stream()),
+          "tb_residual_sandwich_layernorm_rows")
+    return h
+
+
+def token_side_input(x, side_embed, e_off, ids, w_gate, w_proj, norm_w, eps, w_pre=None, b_pre=None, pre_rms=False,
+                     out_dtype=torch.float32):
+    """x += rms_norm(w_proj (gelu_tanh(w_gate x) * side_embed[ids, e_off : e_off + sd])) * norm_w in place (sd = w_gate.shape[0]);
+    with ``w_pre`` also returns the next layer's input: layer_norm(x; w_pre, b_pre), or the RMS norm when ``pre_rms``."""
+    _chk_dev(x, side_embed, ids, w_gate, w_proj, norm_w, w_pre, b_pre)
+    sd, width = w_gate.shape
+    if x.dtype != torch.float32 or x.stride(1) != 1 or x.shape[1] != width or tuple(w_proj.shape) != (width, sd) \
+            or side_embed.shape[1] < e_off + sd or side_embed.stride(1) != 1:
+        raise ValueError("token_side_input: x fp32 [N, width], w_gate [sd, width], w_proj [width, sd], side_embed [vocab, >= e_off + sd]")
+    for t in (side_embed, w_proj, norm_w, w_pre, b_pre):
+        if t is not None and t.dtype != w_gate.dtype:
+            raise TypeError("token_side_input: tensors of one storage type")
+    h = torch.empty(x.shape, dtype=out_dtype, device=x.device) if w_pre is not None else None
+    check(_rl.tb_token_side_input(_p(x), x.stride(0), _p(side_embed), side_embed.stride(0), int(e_off), _p(ids), side_embed.shape[0],
+                                  _p(w_gate), _p(w_proj), _p(norm_w), _dt(w_gate), float(eps), x.shape[0], width, sd, _p(w_pre), _p(b_pre),
+                                  int(bool(pre_rms)), _p(h), _dt(h) if h is not None else 0, h.stride(0) if h is not None else 0,
+                                  _stream()), "tb_token_side_input")
+    return h
+
+
+def rmsnorm_pair_sum(a, b, wa, wb, eps, out_scale):
+    """out_scale * (a / rms(a) * wa + b / rms(b) * wb) over fp32 rows."""
+    _chk_dev(a, b, wa, wb)
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.stride(1) != 1 or b.stride(1) != 1 or a.shape != b.shape \
+            or wa.dtype != wb.dtype:
+        raise ValueError("rmsnorm_pair_sum: two fp32 row sets of one shape, weights of one type")
+    out = torch.empty(a.shape, dtype=torch.float32, device=a.device)
+    check(_rl.tb_rmsnorm_pair_sum(_p(out), out.stride(0), _p(a), a.stride(0), _p(b), b.stride(0), _p(wa), _p(wb), _dt(wa), float(eps),
+                                  float(out_scale), a.shape[0], a.shape[1], _stream()), "tb_rmsnorm_pair_sum")
     return out
 
 
@@ -818,16 +983,19 @@ def moe_linear_tc(xs, w, tile_expert, out_dtype, act=ACT_NONE):
     return out
 
 
-def moe_gemv(a, w, ids, *, a_div, out_dtype, gated=False, act=ACT_NONE):
+def moe_gemv(a, w, ids, *, a_div, out_dtype, gated=False, act=ACT_NONE, gate=GATE_SIGMOID, alpha=1.0, limit=0.0, up_shift=0.0,
+             pair_scale=None):
     """Expert products for few pairs without a plan: pair b against expert ids[b].  gated: w [experts, 2 N, K] and the
-    result is silu(gate) * up; else ``act`` is applied.  Returns None when the streaming kernel does not take the shape."""
+    result is the gated activation (``gate``, alpha, limit, up_shift; the defaults are silu(gate) * up) of the two products, both
+    first multiplied by ``pair_scale[b]`` (fp32) when given; else ``act`` is applied.  Returns None when the streaming kernel
+    does not take the shape."""
     _chk_dev(a, w, ids)
     E, rows_w, K = w.shape
     N = rows_w // 2 if gated else rows_w
     pairs = ids.numel()
     out = torch.empty((pairs, N), dtype=out_dtype, device=a.device)
     rc = _rl.tb_moe_gemv(_p(out), _dt(out), out.stride(0), _p(a), _dt(a), a.stride(0), _p(w), _dt(w), _p(ids), pairs, int(a_div),
-                         N, K, 2 if gated else act, 1.0, 0.0, _stream())
+                         N, K, 2 if gated else act, int(gate), float(alpha), float(limit), float(up_shift), _p(pair_scale), _stream())
     if rc == -3:
         return None
     check(rc, "tb_moe_gemv")
@@ -836,9 +1004,14 @@ def moe_gemv(a, w, ids, *, a_div, out_dtype, gated=False, act=ACT_NONE):
 
 def moe_combine(y, weights, pair_slot=None, add=None):
     """out[n] = add[n] + sum_k weights[n, k] * y[row of pair n * top + k]  (fp32); the pair's row is pair_slot[pair], or the
-    pair's index when ``y`` is in pair order.  ``add``: fp32 [N, width] every token has besides (a shared expert), or None."""
-    _chk_cuda(y, weights, pair_slot, add)
-    rows, top = weights.shape
+    pair's index when ``y`` is in pair order.  ``add``: fp32 [N, width] every token has besides (a shared expert), or None.
+    ``weights`` may be ``(rows, top)`` instead of a tensor: a plain sum."""
+    _chk_cuda(y, pair_slot, add)
+    if isinstance(weights, tuple):
+        (rows, top), weights = weights, None
+    else:
+        _chk_cuda(weights)
+        rows, top = weights.shape
     out = torch.empty((rows, y.shape[1]), dtype=torch.float32, device=y.device)
     if add is not None and (add.dtype != torch.float32 or add.shape != out.shape):
         raise ValueError("moe_combine: add is fp32 [N, width]")
