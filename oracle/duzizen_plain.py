@@ -119,7 +119,7 @@ def tied_window_mixer(h, P, pre, mc, eps):
     T = h.shape[0]
     H, G, d = int(mc["heads"]), int(mc.get("kv_heads", mc["heads"])), int(mc["dim"])
     q, k = h @ P[pre + "q"].T, h @ P[pre + "k"].T
-    if int(mc.get("conv", 1)) > 1:
+    if pre + "q.conv" in P:
         q, k = short_conv(q, P[pre + "q.conv"]), short_conv(k, P[pre + "k.conv"])
     v = k.clone().view(T, G, d)
     q = (rms(q, eps) * P[pre + "q.norm"]).view(T, H, d)
@@ -270,3 +270,107 @@ def duzizen_forward(config, tensors, tokens, return_layers=False):
     trace = []
     z = forward(list(tokens), P, config, trace)
     return (z, torch.stack(trace)) if return_layers else z
+
+
+def random_duzizen(layers, *, width=48, vocab=61, eps=1e-5, side_dim=4, bigram=(13, 5, 3), seed=0, dtype=torch.bfloat16,
+                   spaced_router=False, steady_memory=False):
+    """A small random model.  ``layers``: list of dicts, either
+      {type: "mlstm", heads, dim, vdim, [gate_cap], mlp}
+      {type: "parallel", left: {heads, kv_heads, dim, [conv], [scale], [window], [keep_first], [rot_dims], [rot_base], [scaling]},
+                         right: {heads, dim, vdim, decay, [rot_dims], [rot_base]}, mlp}
+    with mlp: None | ("dense", ff) | ("moe", ff, experts, top, limit).  ``side_dim`` 0: no per-layer token input; ``bigram`` =
+    (buckets, mul_prev, mul_cur) or None.  Returns (config, tensors) in the checkpoint's naming; values are rounded to ``dtype``
+    so that product and oracle start from the same numbers.
+
+    ``spaced_router``: the router's rows are multiples (steps of 0.3) of ONE unit direction and the bias of the norm in front of
+    the feed-forward has a component of 6 along it, so every token ranks the experts alike with logits about 1.8 apart and a
+    run in reduced precision can be compared position by position without a close call deciding which experts ran.
+
+    ``steady_memory``: queries and keys of a matrix memory share a component (every row of W_q and W_k gets 0.5 times ONE unit
+    direction, along which the bias of the norm in front of the mixer has a component of 4), so that n . q stays well away
+    from 0.  With random weights some token's query is nearly orthogonal to n, the read-out divides by a difference of large
+    terms, and a run whose projections see bf16 inputs differs there by far more than rounding — which is no kernel's error."""
+    g = torch.Generator().manual_seed(seed)
+
+    def n(*shape, std=None, mean=0.0):
+        std = std if std is not None else shape[-1] ** -0.5
+        return (torch.randn(*shape, generator=g) * std + mean).to(dtype)
+
+    def lin(out, inp, gain=1.0):
+        return n(out, inp, std=gain * inp ** -0.5)
+
+    t = {"embed": n(vocab, width, std=1.0), "head": n(vocab, width, std=3.0 * width ** -0.5),
+         "final.norm": n(width, std=0.2, mean=1.0), "final.norm.b": n(width, std=0.2)}
+    config = {"architecture": "Duzizen", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": []}
+    if bigram:
+        config["embedding"] = {"bigram": dict(zip(("buckets", "mul_prev", "mul_cur"), bigram))}
+        t["bigram"] = n(bigram[0] + 1, width, std=0.7)
+    if side_dim:
+        config["token_side"] = {"dim": side_dim}
+        t["side.embed"] = n(vocab, side_dim * len(layers), std=1.0)
+    for i, l in enumerate(layers):
+        p = f"l{i}."
+        for k in ("norm1", "norm1b", "norm2", "norm2b"):
+            t[p + k], t[p + k + ".b"] = n(width, std=0.2, mean=1.0), n(width, std=0.2)
+        if l["type"] == "mlstm":
+            H, d, dv = l["heads"], l["dim"], l["vdim"]
+            m = {"heads": H, "dim": d, "vdim": dv, "gate_cap": l.get("gate_cap", 10.0)}
+            t.update({p + "mix.q": lin(H * d, width, 2.0), p + "mix.k": lin(H * d, width, 2.0), p + "mix.v": lin(H * dv, width, 2.0),
+                      p + "mix.g": lin(H * dv, width, 2.0), p + "mix.o": lin(width, H * dv), p + "mix.norm": n(H * dv, std=0.2, mean=1.0),
+                      p + "mix.i": lin(H, width, 3.0), p + "mix.i.b": n(H, std=1.0), p + "mix.f": lin(H, width, 3.0),
+                      p + "mix.f.b": n(H, std=1.0, mean=2.0)})
+            if steady_memory:
+                direction = torch.randn(width, generator=g)
+                direction = direction / direction.norm()
+                for k in ("mix.q", "mix.k"):
+                    t[p + k] = (t[p + k].double() + 0.5 * direction[None, :]).to(dtype)
+                t[p + "norm1.b"] = (t[p + "norm1.b"].double() + 4.0 * direction).to(dtype)
+        else:
+            a, r = l["left"], l["right"]
+            H, G, d = a["heads"], a["kv_heads"], a["dim"]
+            left = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": a.get("scale", d ** -0.5)}
+            if a.get("conv", 0):
+                left["conv"] = a["conv"]
+                t[p + "mix.left.q.conv"], t[p + "mix.left.k.conv"] = n(H * d, a["conv"], std=0.6), n(G * d, a["conv"], std=0.6)
+            if a.get("window", 0):
+                left["mask"] = {"size": a["window"], "keep_first": a.get("keep_first", 0)}
+            if a.get("rot_dims", 0):
+                left["rot"] = {"base": a.get("rot_base", 10000.0), "dims": a["rot_dims"]}
+                if a.get("scaling"):
+                    left["rot"]["scaling"] = dict(zip(("factor", "low", "high", "original"), a["scaling"]))
+            t.update({p + "mix.left.q": lin(H * d, width, 2.0), p + "mix.left.k": lin(G * d, width, 2.0),
+                      p + "mix.left.q.norm": n(H * d, std=0.3, mean=1.5), p + "mix.left.k.norm": n(G * d, std=0.3, mean=1.5),
+                      p + "mix.left.o": lin(width, H * d), p + "mix.left.out": n(width, std=0.2, mean=1.0)})
+            Hr, dr, dvr = r["heads"], r["dim"], r["vdim"]
+            right = {"heads": Hr, "dim": dr, "vdim": dvr, "decay": [float(x) for x in r["decay"]]}
+            if r.get("rot_dims", 0):
+                right["rot"] = {"base": r.get("rot_base", 10000.0), "dims": r["rot_dims"]}
+            t.update({p + "mix.right.q": lin(Hr * dr, width, 2.0), p + "mix.right.k": lin(Hr * dr, width, 2.0),
+                      p + "mix.right.v": lin(Hr * dvr, width, 2.0), p + "mix.right.g": lin(Hr * dvr, width, 2.0),
+                      p + "mix.right.o": lin(width, Hr * dvr), p + "mix.right.out": n(width, std=0.2, mean=1.0)})
+            m = {"left": left, "right": right}
+        mlp = None
+        if l.get("mlp"):
+            if l["mlp"][0] == "dense":
+                ff = l["mlp"][1]
+                mlp = {"kind": "dense", "ff": ff}
+                t.update({p + "mlp.gate": lin(ff, width, 2.0), p + "mlp.up": lin(ff, width, 2.0), p + "mlp.down": lin(width, ff)})
+            else:
+                _, ff, E, top, limit = l["mlp"]
+                mlp = {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": E, "top": top}}
+                t[p + "mlp.router"] = lin(E, width, 3.0)
+                if spaced_router:
+                    direction = torch.randn(width, generator=g)
+                    direction = direction / direction.norm()
+                    factors = torch.randperm(E, generator=g).double() - (E - 1) / 2
+                    t[p + "mlp.router"] = (factors[:, None] * direction[None, :] * 0.3).to(dtype)
+                    t[p + "norm2.b"] = (t[p + "norm2.b"].double() + 6.0 * direction).to(dtype)
+                for e in range(E):
+                    t.update({f"{p}mlp.e{e}.gate": lin(ff, width, 3.0), f"{p}mlp.e{e}.up": lin(ff, width, 3.0), f"{p}mlp.e{e}.down": lin(width, ff)})
+        else:
+            for k in ("norm2", "norm2b"):
+                del t[p + k], t[p + k + ".b"]
+        if side_dim:
+            t.update({p + "side.gate": lin(side_dim, width, 2.0), p + "side.proj": lin(width, side_dim), p + "side.norm": n(width, std=0.2, mean=0.7)})
+        config["layers"].append({"type": l["type"], "mixer": m, "mlp": mlp})
+    return config, t

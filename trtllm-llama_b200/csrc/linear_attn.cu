@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(32) mlstm_gates_kernel(float* log_ab, float* m
     if (lane == 0) mp = m;
     if (live) {
       const int64_t o = (int64_t) (start + t) * a.heads + h;
-      log_ab[2 * o] = fg + mp - mt;
+      log_ab[2 * o] = fminf(fg + mp - mt, 0.f);      // m_t >= f_t + m_(t-1); the scan's sums may round it a few ulp the other way
       log_ab[2 * o + 1] = ig - mt;
       m_out[o] = mt;
     }
