@@ -703,9 +703,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-tp-parity", action="store_true")
     ap.add_argument("--nccl-only", action="store_true", help="tensor parallel: use the NCCL AllReduce plugin on the decode path too")
-    ap.add_argument("--model", default=None, choices=["zobasun", "nililix", "mimolix"],
+    ap.add_argument("--model", default=None, choices=["zobasun", "nililix", "mimolix", "duzizen"],
                     help="instead of the default workload: prefill / decode throughput of this in-flight served design "
-                         "beside a LLaMA engine of equal size (mimolix: beside nililix at equal size), with every operator's "
+                         "beside a LLaMA engine of equal size (mimolix: beside nililix, duzizen: beside mimolix, at equal size), with every operator's "
                          "distance from its roofline")
     ap.add_argument("--model-sizes", default=None, help="comma list of sizes for --model (default: all)")
     args = ap.parse_args()

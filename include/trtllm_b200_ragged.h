@@ -304,12 +304,13 @@ int tb_gated_rmsnorm_heads(void* out, int dtype, const float* o, const float* ga
  * (<= 0), ln b_t; or NULL, then a_t = head_decay[h] (fp32 [heads]) and b_t = 1.  ones_col != 0: one more value column follows
  * the values whose v is 1 at every row (its state is sum of weighted keys: the normaliser of an mLSTM), vcols = vdim + 1.
  * state: slot s at state + s * state_stride, [heads, vcols, dim] (a column's dim elements contiguous); zeros at a sequence's
- * first position.  out fp32 [N, heads, vcols].  max_len: the longest seq_len (host): from 4 rows on (dim <= 256) the rows are
+ * first position.  q_scale: a factor on every query (1: none).  out fp32 [N, heads, vcols].  max_len: the longest seq_len
+ * (host): from 4 rows on (dim <= 256) the rows are
  * resolved 32 at a time from the portion's first row (the same recurrence up to fp32 rounding), else row by row. */
 int tb_decay_attention_scan(float* out, const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
                             const float* log_ab, const float* head_decay, float* state, int64_t state_stride, const int* seq_start,
                             const int* seq_len, const int* seq_past, const int* seq_slot, int rows, int seqs, int heads, int dim,
-                            int vdim, int ones_col, int max_len, tb_stream_t stream);
+                            int vdim, int ones_col, float q_scale, int max_len, tb_stream_t stream);
 /* A/B switch for tests and measurements: 1 keeps tb_decay_attention_scan row by row; 0: by max_len (default). */
 int tb_decay_scan_set_mode(int mode);
 /* Gates of an mLSTM matrix memory.  Per row and head, from proj (fp32, row stride ldp): i = cap * tanh((proj[col_i + h] + bias_i[h])

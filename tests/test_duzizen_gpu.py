@@ -408,9 +408,13 @@ def _mixer_alone(dtype, layer, lens, what, fn, pre, sub=None):
     model = build_duzizen(cfg, t, dtype, "cuda")
     sess, ctx = _mixer_ctx(model, lens)
     h = torch.randn(sum(lens), 40, generator=torch.Generator().manual_seed(4))
+    from trtllm_llama_b200 import ops
     mixer = model.layers[0]["mixer"]
-    mixer = getattr(mixer, sub) if sub else mixer
-    got = mixer.forward(h.to(dtype).cuda(), ctx)
+    if sub:           # one of two mixers side by side: its rows of the pair's stacked input projection
+        proj = ops.linear(h.to(dtype).cuda(), mixer.w_in, out_dtype=torch.float32)
+        got = getattr(mixer, sub).forward(h.to(dtype).cuda(), ctx, proj=proj[:, :mixer.split] if sub == "left" else proj[:, mixer.split:])
+    else:
+        got = mixer.forward(h.to(dtype).cuda(), ctx)
     P, at = {k: v.double() for k, v in t.items()}, 0
     mc = cfg["layers"][0]["mixer"]
     for n in lens:

@@ -113,6 +113,7 @@ struct ScanArgs {
   float* state; int64_t state_stride;                 // state + slot * state_stride: [heads, vcols, dim]
   const int *seq_start, *seq_len, *seq_past, *seq_slot;
   int heads, dim, vdim, vcols;                        // vcols = vdim + 1 when a column of ones follows the values
+  float q_scale;                                      // every query is multiplied by it as it is read
 };
 
 constexpr int kRowWarps = 4;
@@ -147,7 +148,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) decay_scan_rows_kernel(float* 
         o = fmaf(s[i], qr[d], o);
       }
     }
-    o = warp_sum(o);
+    o = warp_sum(o) * a.q_scale;
     if (lane == 0) out[(row * a.heads + h) * a.vcols + col] = o;
   }
 #pragma unroll
@@ -195,7 +196,7 @@ __global__ void __launch_bounds__(256) decay_scan_chunk_kernel(float* out, ScanA
     for (int idx = threadIdx.x; idx < kChunk * DP; idx += 256) {
       const int t = idx / DP, d = idx % DP;
       const bool ok = t < n && d < a.dim;
-      Qs[t * LD + d] = ok ? a.q[(row0 + t) * a.ldq + (int64_t) h * a.dim + d] : 0.f;
+      Qs[t * LD + d] = ok ? a.q[(row0 + t) * a.ldq + (int64_t) h * a.dim + d] * a.q_scale : 0.f;
       Ks[t * LD + d] = ok ? a.k[(row0 + t) * a.ldk + (int64_t) h * a.dim + d] : 0.f;
     }
     for (int idx = threadIdx.x; idx < kChunk * 32; idx += 256) {
@@ -407,12 +408,13 @@ extern "C" int tb_decay_scan_set_mode(int mode) { g_decay_scan_mode = mode; retu
 extern "C" int tb_decay_attention_scan(float* out, const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
                                        const float* log_ab, const float* head_decay, float* state, int64_t state_stride,
                                        const int* seq_start, const int* seq_len, const int* seq_past, const int* seq_slot, int rows,
-                                       int seqs, int heads, int dim, int vdim, int ones_col, int max_len, tb_stream_t stream) {
+                                       int seqs, int heads, int dim, int vdim, int ones_col, float q_scale, int max_len,
+                                       tb_stream_t stream) {
   if (!out || !q || !k || !v || !state || !seq_start || !seq_len || !seq_past || !seq_slot || (!log_ab && !head_decay)) return -1;
   if (heads <= 0 || dim <= 0 || dim > 1024 || vdim <= 0 || rows < 0 || seqs < 0 || seqs > 65535 || heads > 65535) return -1;
   if (rows == 0 || seqs == 0) return 0;
   ScanArgs a{q, k, v, ldq, ldk, ldv, log_ab, head_decay, state, state_stride, seq_start, seq_len, seq_past, seq_slot, heads, dim, vdim,
-             vdim + (ones_col ? 1 : 0)};
+             vdim + (ones_col ? 1 : 0), q_scale};
   cudaStream_t st = (cudaStream_t) stream;
   if (g_decay_scan_mode != 1 && max_len >= 4 && dim <= 256) {
     const int dpt = (dim + 7) / 8;

@@ -170,9 +170,12 @@ class WindowedAttention:
     def conv_state(self):
         return None if self.whole_norm and self.taps == 1 else (self.taps, self.channels, 0)
 
-    def forward(self, x, ctx, rep=0):
+    def forward(self, x, ctx, rep=0, proj=None):
+        """``proj``: the rows' input projection (fp32 [N, >= w_in rows], any row stride) when a caller has already run it as part
+        of a wider stacked product; ``x`` is then not read."""
         n, key = x.shape[0], (self.index, rep)
-        proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
+        if proj is None:
+            proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
         table = ctx.rope_table(self.rot_dims, self.rot_base, self.rot_scaling) if self.rot_dims else None
         if self.whole_norm:
             q = ops.qk_conv_norm_rope_append(proj, self.conv_w, self.q_norm, self.k_norm, self.eps,
@@ -326,17 +329,18 @@ class Retention:
     def conv_state(self):
         return (1, 0, self.heads * self.vdim * self.dim)
 
-    def forward(self, x, ctx, rep=0, project=True):
-        """-> W_o of the gated, normalised read-out; ``project`` False: the read-out itself [N, heads * vdim] in the storage type."""
+    def forward(self, x, ctx, rep=0, proj=None):
+        """``proj``: the rows' input projection (fp32 [N, >= w_in rows], any row stride) when a caller has already run it as part
+        of a wider stacked product; ``x`` is then not read."""
         n, H = x.shape[0], self.heads
-        proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
+        if proj is None:
+            proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
         table = ctx.rope_table(self.rot_dims, self.rot_base, self.rot_scaling) if self.rot_dims else None
         qk = ops.rope_heads(proj, table, 2 * H, self.dim, self.rot_dims, self.rot_layout, split=H, scale_lo=1.0, scale_hi=self.k_scale)
         o = ops.decay_attention_scan(qk, qk[:, H * self.dim:], proj[:, self.col_v:self.col_g], ctx.states[(self.index, rep)][1],
                                      ctx.batch, H, self.dim, self.vdim, head_decay=self.decay)
         y = ops.head_norm_gate(o, self.vdim, self.eps, self.dtype, gate=proj[:, self.col_g:], gate_act="silu")
-        y = y.view(n, H * self.vdim)
-        return ops.linear(y, self.w_o, out_dtype=torch.float32) if project else y
+        return ops.linear(y.view(n, H * self.vdim), self.w_o, out_dtype=torch.float32)
 
 
 class MatrixMemory:
@@ -381,9 +385,8 @@ class MatrixMemory:
         proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
         rec = ctx.states[(self.index, rep)][1]
         log_ab, m = ops.mlstm_gates(proj, self.col_i, self.col_f, self.b_i, self.b_f, self.gate_cap, rec[:, self.state_cols:], ctx.batch, H)
-        q = ops.rope_heads(proj, None, H, self.dim, 0, ops.ROPE_HALF, scale_hi=self.dim ** -0.5)
-        o = ops.decay_attention_scan(q, proj[:, self.col_k:self.col_v], proj[:, self.col_v:self.col_g], rec, ctx.batch, H, self.dim,
-                                     self.vdim, log_ab=log_ab, ones_col=True)
+        o = ops.decay_attention_scan(proj, proj[:, self.col_k:self.col_v], proj[:, self.col_v:self.col_g], rec, ctx.batch, H, self.dim,
+                                     self.vdim, log_ab=log_ab, ones_col=True, q_scale=self.dim ** -0.5)
         y = ops.head_norm_gate(o, self.vdim, self.eps, self.dtype, w=self.norm, w_per_head=True, gate=proj[:, self.col_g:self.col_i],
                                gate_act="sigmoid", m=m, den_eps=self.den_eps)
         return ops.linear(y.view(n, H * self.vdim), self.w_o, out_dtype=torch.float32)
@@ -392,7 +395,9 @@ class MatrixMemory:
 class SideBySideMixers:
     """Two sequence mixers that read the same input; the result is ``mult`` * (rms_norm(left(h)) * w_left + rms_norm(right(h)) *
     w_right), each output normalised over the model width with its own weight.  Caches and states are the union of the two
-    (at most one of them may page a cache, at most one may carry convolution inputs, at most one a recurrent state)."""
+    (at most one of them may page a cache, at most one may carry convolution inputs, at most one a recurrent state).
+    Mixers that open with one stacked input projection (``w_in``, and ``forward(..., proj=)``) share ONE product against
+    [left rows | right rows]: the input is read once and a generation step launches one streaming product instead of two."""
 
     def __init__(self, index, left, right, *, w_left, w_right, eps, mult=0.5):
         self.index, self.left, self.right, self.w_left, self.w_right = index, left, right, w_left, w_right
@@ -402,6 +407,11 @@ class SideBySideMixers:
             raise NotImplementedError(f"layer {index}: both side-by-side mixers want the same kind of cache or state")
         conv = cl if cl[0] > 1 else cr
         self._state = (conv[0], conv[1], cl[2] or cr[2]) if (conv[0] > 1 or cl[2] or cr[2]) else None
+        self.w_in = None
+        if getattr(left, "w_in", None) is not None and getattr(right, "w_in", None) is not None and left.w_in.dtype == right.w_in.dtype:
+            self.split = left.w_in.shape[0]
+            self.w_in = torch.cat([left.w_in, right.w_in], dim=0).contiguous()
+            left.w_in = right.w_in = None                    # held once, stacked
 
     def cache_entries(self):
         return self.left.cache_entries() or self.right.cache_entries()
@@ -410,8 +420,13 @@ class SideBySideMixers:
         return self._state
 
     def forward(self, x, ctx, rep=0):
-        a = self.left.forward(x, ctx, rep)
-        b = self.right.forward(x, ctx, rep)
+        if self.w_in is not None:
+            proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
+            a = self.left.forward(x, ctx, rep, proj=proj[:, :self.split])
+            b = self.right.forward(x, ctx, rep, proj=proj[:, self.split:])
+        else:
+            a = self.left.forward(x, ctx, rep)
+            b = self.right.forward(x, ctx, rep)
         return ops.rmsnorm_pair_sum(a, b, self.w_left, self.w_right, self.eps, self.mult)
 
 

@@ -148,6 +148,64 @@ def random_mimolix(torch, s, seed=0):
     return cfg, t
 
 
+DUZIZEN_SIZES = {
+    # window attention: heads x dim over kv_heads (values = keys); retention: r_heads x (r_dim, r_vdim); matrix memory: m_heads x
+    # (m_dim, m_vdim); feed-forward: one gated GELU layer of ff, then `experts` clamped experts of eff with `top` active
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, keep_first=4, r_heads=8, r_dim=128, r_vdim=256, m_heads=16,
+                  m_dim=128, m_vdim=128, experts=16, top=4, eff=1408, ff=5632, side=128, buckets=50021, vocab=32000),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, window=1024, keep_first=4, r_heads=16, r_dim=128, r_vdim=256, m_heads=32,
+                  m_dim=128, m_vdim=128, experts=16, top=4, eff=2752, ff=11008, side=256, buckets=50021, vocab=32000),
+}
+
+
+def random_duzizen(torch, s, seed=0):
+    """config + bf16 tensors of a 6-layer stack [pair, memory, pair, memory, pair, memory] (pair = window attention beside a
+    retention); the first layer with a gated GELU feed-forward, the others with routed experts."""
+    g = torch.Generator().manual_seed(seed)
+    W, H, G, d = s["width"], s["heads"], s["kv_heads"], s["dim"]
+    RH, rd, rdv, MH, md, mdv = s["r_heads"], s["r_dim"], s["r_vdim"], s["m_heads"], s["m_dim"], s["m_vdim"]
+
+    def n(*shape, std=None):
+        std = std if std is not None else shape[-1] ** -0.5
+        return (torch.randn(*shape, generator=g) * std).to(torch.bfloat16)
+
+    left = dict(heads=H, kv_heads=G, dim=d, vdim=d, conv=4, scale=d ** -0.5, mask=dict(size=s["window"], keep_first=s["keep_first"]),
+                rot=dict(base=10000.0, dims=d // 2, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    right = dict(heads=RH, dim=rd, vdim=rdv, decay=[1.0 - 2.0 ** (-5 - 5 * i / max(RH - 1, 1)) for i in range(RH)],
+                 rot=dict(base=10000.0, dims=rd))
+    mem = dict(heads=MH, dim=md, vdim=mdv, gate_cap=20.0)
+    moe = dict(kind="moe", expert=dict(ff=s["eff"], limit=7.0), router=dict(experts=s["experts"], top=s["top"]))
+    kinds = ["parallel", "mlstm"] * 3
+    layers = [dict(type=ty, mixer=dict(left=left, right=right) if ty == "parallel" else dict(mem),
+                   mlp=dict(kind="dense", ff=s["ff"]) if i == 0 else moe) for i, ty in enumerate(kinds)]
+    cfg = dict(architecture="Duzizen", vocab=s["vocab"], width=W, norm=dict(eps=1e-5), token_side=dict(dim=s["side"]),
+               embedding=dict(bigram=dict(buckets=s["buckets"], mul_prev=31, mul_cur=17)), layers=layers)
+    t = {"embed": n(s["vocab"], W, std=1.0), "bigram": n(s["buckets"] + 1, W, std=0.5), "side.embed": n(s["vocab"], s["side"] * len(layers), std=1.0),
+         "head": n(s["vocab"], W), "final.norm": n(W, std=0.1) + 1, "final.norm.b": n(W, std=0.1)}
+    for i, l in enumerate(layers):
+        p = f"l{i}."
+        for k in ("norm1", "norm1b", "norm2", "norm2b"):
+            t[p + k], t[p + k + ".b"] = n(W, std=0.1) + 1, n(W, std=0.1)
+        if l["type"] == "parallel":
+            t.update({p + "mix.left.q": n(H * d, W), p + "mix.left.k": n(G * d, W), p + "mix.left.q.conv": n(H * d, 4, std=0.5),
+                      p + "mix.left.k.conv": n(G * d, 4, std=0.5), p + "mix.left.q.norm": n(H * d, std=0.1) + 1,
+                      p + "mix.left.k.norm": n(G * d, std=0.1) + 1, p + "mix.left.o": n(W, H * d), p + "mix.left.out": n(W, std=0.1) + 1,
+                      p + "mix.right.q": n(RH * rd, W), p + "mix.right.k": n(RH * rd, W), p + "mix.right.v": n(RH * rdv, W),
+                      p + "mix.right.g": n(RH * rdv, W), p + "mix.right.o": n(W, RH * rdv), p + "mix.right.out": n(W, std=0.1) + 1})
+        else:
+            t.update({p + "mix.q": n(MH * md, W), p + "mix.k": n(MH * md, W), p + "mix.v": n(MH * mdv, W), p + "mix.g": n(MH * mdv, W),
+                      p + "mix.o": n(W, MH * mdv), p + "mix.norm": n(MH * mdv, std=0.1) + 1, p + "mix.i": n(MH, W), p + "mix.i.b": n(MH, std=0.5),
+                      p + "mix.f": n(MH, W), p + "mix.f.b": n(MH, std=0.5) + 3})
+        if l["mlp"]["kind"] == "dense":
+            t.update({p + "mlp.gate": n(s["ff"], W), p + "mlp.up": n(s["ff"], W), p + "mlp.down": n(W, s["ff"])})
+        else:
+            t[p + "mlp.router"] = n(s["experts"], W)
+            for e in range(s["experts"]):
+                t.update({f"{p}mlp.e{e}.gate": n(s["eff"], W), f"{p}mlp.e{e}.up": n(s["eff"], W), f"{p}mlp.e{e}.down": n(W, s["eff"])})
+        t.update({p + "side.gate": n(s["side"], W), p + "side.proj": n(W, s["side"]), p + "side.norm": n(W, std=0.1) + 1})
+    return cfg, t
+
+
 class OpTimer:
     """Wraps the ragged operators of ``ops`` with CUDA-event timers and the bytes / flops each call moves."""
 
@@ -155,7 +213,9 @@ class OpTimer:
              "latent_attention", "causal_conv1d", "rglru_scan", "qkv_conv_rope_append", "window_attention", "moe_route",
              "moe_plan", "moe_linear", "moe_linear_tc", "moe_gemv", "moe_gather_rows", "moe_combine", "add_row_vector", "tanh_cap",
              "residual_norm_rows", "layernorm_rows", "residual_layernorm_rows", "concat_rows", "qk_norm_append", "diff_combine",
-             "delta_prepare", "delta_rule_scan", "gated_rmsnorm_heads", "moe_route_softmax")
+             "delta_prepare", "delta_rule_scan", "gated_rmsnorm_heads", "moe_route_softmax", "embed_bigram", "qk_conv_norm_rope_append",
+             "rope_heads", "mlstm_gates", "decay_attention_scan", "head_norm_gate", "residual_sandwich_layernorm_rows",
+             "token_side_input", "rmsnorm_pair_sum")
 
     def __init__(self, torch, ops):
         self.torch, self.ops, self.rec, self.saved = torch, ops, [], {}
@@ -194,7 +254,7 @@ class OpTimer:
             H, d = q.shape[1], q.shape[2]
             vsh = kw.get("v_share", 1)
             pos = batch._host[batch.num_rows * 2:batch.num_rows * 3].double()
-            keys = float(((pos + 1).clamp(max=window) if window else (pos + 1)).sum())
+            keys = float(((pos + 1).clamp(max=window + kw.get("keep_first", 0)) if window else (pos + 1)).sum())
             seq = batch._host[batch.num_rows:batch.num_rows * 2].tolist()
             first, last = {}, {}
             for sq, p in zip(seq, pos.tolist()):
@@ -217,6 +277,26 @@ class OpTimer:
             u, bg, state, batch, H, G, d, dv = args
             # the state of every sequence in the step is read and written once; rows in and out once
             return name, 6.0 * u.shape[0] * H * d * dv, nb(u, bg, out) + 2 * batch.num_seqs * H * d * dv * 4
+        if name == "decay_attention_scan":
+            q, k, v, state, batch, H, d, dv = args[:8]
+            vc = dv + (1 if kw.get("ones_col") else 0)
+            # rows in and out once; the state of every sequence in the step read and written once
+            return name, 4.0 * q.shape[0] * H * d * vc, q.shape[0] * H * (2 * d + dv + vc) * 4 + 2 * batch.num_seqs * H * d * vc * 4
+        if name == "qk_conv_norm_rope_append":
+            proj, pool, H, G, d, dv = args[0], args[8], args[11], args[12], args[13], args[14]
+            return name, 0.0, proj.shape[0] * ((H + G) * d * 4 + (H * d + G * (d + dv)) * pool.element_size())
+        if name == "rope_heads":
+            return name, 0.0, args[0].shape[0] * args[2] * args[3] * 8
+        if name == "mlstm_gates":
+            return name, 0.0, args[0].shape[0] * args[8] * (2 + 3) * 4
+        if name == "head_norm_gate":
+            o, dv = args[0], args[1]
+            return name, 0.0, nb(o, out) + (o.shape[0] * o.shape[1] * dv * 4 if kw.get("gate") is not None else 0)
+        if name == "token_side_input":
+            x, wg, wp = args[0], args[4], args[5]
+            return name, 0.0, 2 * nb(x) + nb(wg, wp, out) + x.shape[0] * wg.shape[0] * wg.element_size()
+        if name == "residual_sandwich_layernorm_rows":
+            return name, 0.0, 2 * nb(args[0]) + nb(args[1], out)
         if name == "delta_prepare":
             return name, 0.0, args[0].shape[0] * (2 * kw.get("C", args[8] * args[11] + 2 * args[9] * args[10]) * 4) + nb(*out[1:])
         if name == "qk_norm_append":
@@ -640,14 +720,140 @@ def bench_mimolix_size(torch, name, steps, warmup, S=2048, B=4):
     return res
 
 
+def bench_duzizen_size(torch, name, steps, warmup, S=2048, B=4):
+    """Duzizen beside Mimolix (the closest design served in-flight: layer norms with biases, a recurrence with a matrix state per
+    head beside softmax attention, routed experts) at equal width, expert sizes, vocabulary and number of layer runs; then the
+    like kernels alone on the same shapes: the decayed linear attention (matrix memory, retention) against the delta rule, the
+    window attention with kept first tokens against the plain window, the two front kernels of the attention, the residual steps."""
+    from . import ops
+    from .inflight import RaggedBatch
+    from .models.duzizen import build_duzizen
+    from .models.mimolix import build_mimolix
+    s, peaks = DUZIZEN_SIZES[name], _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    cfg, tensors = random_duzizen(torch, s)
+    model = build_duzizen(cfg, tensors, torch.bfloat16, "cuda")
+    del tensors
+    res = {"size": dict(s), "layers": [l["type"] for l in cfg["layers"]], "layer_runs": len(model.runs), "prefill_tokens": S,
+           "decode_batch": B, "decode_context": S}
+    res["duzizen"] = _serve(torch, ops, model, s["vocab"], S, B, steps, warmup, flush, peaks)
+    del model
+    torch.cuda.empty_cache()
+    ms = MIMOLIX_SIZES[name]
+    mcfg, mtensors = random_mimolix(torch, ms)
+    mmodel = build_mimolix(mcfg, mtensors, torch.bfloat16, "cuda")
+    del mtensors
+    res["mimolix"] = _serve(torch, ops, mmodel, ms["vocab"], S, B, steps, warmup, flush, peaks)
+    res["mimolix"]["layer_runs"] = len(mmodel.runs)
+    del mmodel
+    torch.cuda.empty_cache()
+
+    like = {}
+    page = 64
+    nblk = -(-S // page)
+    pb = RaggedBatch([([0] * S, 0, 0, list(range(nblk)))], [], "cuda")
+    db = RaggedBatch([([0], S - 1, b, list(range(b * nblk, (b + 1) * nblk))) for b in range(B)], [], "cuda")
+    hbm, tfl = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+
+    def scan(tag, H, d, dv, ones, gated):
+        """prompt and generation step of the decayed linear attention: bytes of rows and state against the copy roofline, and
+        the fp32 multiply-adds it runs (4 per state element and token) against nothing — CUDA cores, no tensor-core peak applies"""
+        vc = dv + (1 if ones else 0)
+        q, k, v = (torch.randn(S, H * n_, device="cuda") * 0.05 for n_ in (d, d, dv))
+        lab = -torch.rand(S, H, 2, device="cuda") * 0.1 if gated else None
+        dec = None if gated else torch.full((H,), 0.98, device="cuda")
+        state = torch.zeros(B + 1, H * vc * d, device="cuda")
+        t = _time_kernel(torch, lambda: ops.decay_attention_scan(q, k, v, state, pb, H, d, dv, log_ab=lab, head_decay=dec, ones_col=ones), steps, warmup, flush)
+        by = S * H * (2 * d + dv + vc) * 4 + 2 * H * d * vc * 4
+        like[tag + "_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(by / hbm / t, 3), "fp32_tflops": round(4.0 * S * H * d * vc / t / 1e12, 2)}
+        qd, kd, vd = q[:B].contiguous(), k[:B].contiguous(), v[:B].contiguous()
+        labd = lab[:B].contiguous() if gated else None
+        t = _time_kernel(torch, lambda: ops.decay_attention_scan(qd, kd, vd, state, db, H, d, dv, log_ab=labd, head_decay=dec, ones_col=ones), steps, warmup, flush)
+        by = 2 * B * H * d * vc * 4
+        like[tag + "_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(by / hbm / t, 3), "state_bytes": by}
+
+    scan("matrix_memory", s["m_heads"], s["m_dim"], s["m_vdim"], True, True)
+    scan("retention", s["r_heads"], s["r_dim"], s["r_vdim"], False, False)
+    # the delta rule on Mimolix' shapes (the recurrence of the closest model)
+    DH, DG, dd, ddv = ms["d_heads"], ms["d_kv_heads"], ms["d_dim"], ms["d_vdim"]
+    C = 2 * DG * dd + DH * ddv
+    u, bg = torch.randn(S, C, device="cuda") * 0.05, torch.rand(S, 2 * DH, device="cuda")
+    state = torch.zeros(B + 1, DH * ddv * dd, device="cuda")
+    t = _time_kernel(torch, lambda: ops.delta_rule_scan(u, bg, state, pb, DH, DG, dd, ddv), steps, warmup, flush)
+    by = (u.numel() + bg.numel() + S * DH * ddv) * 4 + 2 * DH * dd * ddv * 4
+    like["delta_rule_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(by / hbm / t, 3), "fp32_tflops": round(6.0 * S * DH * dd * ddv / t / 1e12, 2)}
+    ud, bgd = u[:B].contiguous(), bg[:B].contiguous()
+    t = _time_kernel(torch, lambda: ops.delta_rule_scan(ud, bgd, state, db, DH, DG, dd, ddv), steps, warmup, flush)
+    by = 2 * B * DH * dd * ddv * 4
+    like["delta_rule_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(by / hbm / t, 3), "state_bytes": by}
+    del u, bg, state
+    # window attention: with kept first tokens (values = keys) against the same kernel without them
+    H, G, d, win, keep = s["heads"], s["kv_heads"], s["dim"], s["window"], s["keep_first"]
+    pool = torch.randn((B * nblk * page, 2 * G * d), device="cuda").bfloat16()
+    q = torch.randn(S, H, d, device="cuda").bfloat16()
+    zeros = torch.zeros(H, device="cuda")
+    pos = torch.arange(S, dtype=torch.float64)
+    for tag, kf in (("window_attention_kept_first", keep), ("window_attention_plain", 0)):
+        keys = float((pos + 1).clamp(max=win + kf).sum())
+        t = _time_kernel(torch, lambda: ops.window_attention(q, pool, pb, page, G, d, 0.1, win, sink=zeros, keep_first=kf), steps, warmup, flush)
+        like[tag + "_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(2.0 * keys * H * 2 * d / tfl / t, 3)}
+        qd = q[:B].contiguous()
+        t = _time_kernel(torch, lambda: ops.window_attention(qd, pool, db, page, G, d, 0.1, win, sink=zeros, keep_first=kf), steps, warmup, flush)
+        cb = B * min(S, win + kf) * 2 * G * d * 2
+        like[tag + "_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(cb / hbm / t, 3), "cache_bytes": cb}
+    # the attention's front kernel: convolution + whole-projection norm + rotation + paged store, against convolution + rotation + store
+    Cq = (H + G) * d
+    proj = torch.randn(S, Cq + G * d, device="cuda")
+    conv = torch.randn(Cq, 4, device="cuda").bfloat16()
+    conv3 = torch.randn(Cq + G * d, 4, device="cuda").bfloat16()
+    nq, nk = torch.ones(H * d, device="cuda").bfloat16(), torch.ones(G * d, device="cuda").bfloat16()
+    st, st3 = torch.zeros(B + 1, 3, Cq, device="cuda"), torch.zeros(B + 1, 3, Cq + G * d, device="cuda")
+    table = ops.rope_table(pb.tok_pos, d // 2, 10000.0)
+    t = _time_kernel(torch, lambda: ops.qk_conv_norm_rope_append(proj, conv, nq, nk, 1e-5, st, table, d // 2, pool, pb, page, H, G, d, d, True), steps, warmup, flush)
+    by = S * (Cq * 4 + (H * d + 2 * G * d) * 2)
+    like["conv_norm_rope_append"] = {"us": round(t * 1e6, 1), "of_roofline": round(by / hbm / t, 3)}
+    t = _time_kernel(torch, lambda: ops.qkv_conv_rope_append(proj, conv3, st3, table, d // 2, pool, pb, page, H, G, d, d), steps, warmup, flush)
+    by = S * (Cq + G * d) * (4 + 2)
+    like["nililix_conv_rope_append"] = {"us": round(t * 1e6, 1), "of_roofline": round(by / hbm / t, 3)}
+    del pool, q, proj
+    # residual steps and the norms behind the recurrences
+    W = s["width"]
+    x, y1, y2 = (torch.randn(S, W, device="cuda") for _ in range(3))
+    w, b = torch.ones(W, device="cuda").bfloat16(), torch.zeros(W, device="cuda").bfloat16()
+    t = _time_kernel(torch, lambda: ops.residual_sandwich_layernorm_rows(x, y1, w, b, 1.0, 1e-5, w, b, torch.bfloat16), steps, warmup, flush)
+    like["residual_sandwich_layernorm"] = {"us": round(t * 1e6, 1), "of_roofline": round(S * W * (3 * 4 + 2) / hbm / t, 3)}
+    t = _time_kernel(torch, lambda: ops.residual_layernorm_rows(x, y1, y2, 0.7, w, b, 1e-6, torch.bfloat16), steps, warmup, flush)
+    like["mimolix_residual_layernorm"] = {"us": round(t * 1e6, 1), "of_roofline": round(S * W * (4 * 4 + 2) / hbm / t, 3)}
+    t = _time_kernel(torch, lambda: ops.rmsnorm_pair_sum(y1, y2, w, w, 1e-5, 0.5), steps, warmup, flush)
+    like["pair_norm_mean"] = {"us": round(t * 1e6, 1), "of_roofline": round(S * W * 3 * 4 / hbm / t, 3)}
+    sd = s["side"]
+    se, wg, wp = torch.randn(s["vocab"], 6 * sd, device="cuda").bfloat16(), torch.randn(sd, W, device="cuda").bfloat16() * W ** -0.5, torch.randn(W, sd, device="cuda").bfloat16()
+    ids = torch.randint(0, s["vocab"], (S,), device="cuda", dtype=torch.int32)
+    t = _time_kernel(torch, lambda: ops.token_side_input(x, se, sd, ids, wg, wp, w, 1e-5, w_pre=w, b_pre=b, out_dtype=torch.bfloat16), steps, warmup, flush)
+    like["token_side_input"] = {"us": round(t * 1e6, 1), "of_roofline": round((S * W * (2 * 4 + 2) + 2 * sd * W * 2) / hbm / t, 3)}
+    MH, mdv = s["m_heads"], s["m_vdim"]
+    o, gate, mm = torch.randn(S, MH, mdv + 1, device="cuda"), torch.randn(S, MH * mdv, device="cuda"), torch.randn(S, MH, device="cuda")
+    wn = torch.ones(MH * mdv, device="cuda").bfloat16()
+    t = _time_kernel(torch, lambda: ops.head_norm_gate(o, mdv, 1e-5, torch.bfloat16, w=wn, w_per_head=True, gate=gate, gate_act="sigmoid", m=mm), steps, warmup, flush)
+    like["head_norm_gate"] = {"us": round(t * 1e6, 1), "of_roofline": round(S * MH * mdv * (4 + 4 + 2) / hbm / t, 3)}
+    o2, wv = torch.randn(S, DH, ddv, device="cuda"), torch.ones(ddv, device="cuda").bfloat16()
+    g2 = torch.randn(S, DH * ddv, device="cuda")
+    t = _time_kernel(torch, lambda: ops.gated_rmsnorm_heads(o2, wv, 1e-6, torch.bfloat16, gate=g2), steps, warmup, flush)
+    like["mimolix_gated_rmsnorm_heads"] = {"us": round(t * 1e6, 1), "of_roofline": round(S * DH * ddv * (4 + 4 + 2) / hbm / t, 3)}
+    res["like_kernels"] = like
+    res["peaks"] = peaks
+    torch.cuda.empty_cache()
+    return res
+
+
 def run(args):
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("bench.py --model needs a B200 (sm_100a): there is no CPU path")
     sizes, fn = {"nililix": (NILILIX_SIZES, bench_nililix_size), "mimolix": (MIMOLIX_SIZES, bench_mimolix_size),
-                 "zobasun": (SIZES, bench_size)}[args.model]
+                 "zobasun": (SIZES, bench_size), "duzizen": (DUZIZEN_SIZES, bench_duzizen_size)}[args.model]
     names = args.model_sizes.split(",") if args.model_sizes else list(sizes)
-    out = {"bench": "model_compare", "model": args.model, "dtype": "bf16" if args.model == "mimolix" else "bf16 (llama: fp16)", "data": "synthetic",
+    out = {"bench": "model_compare", "model": args.model, "dtype": "bf16" if args.model in ("mimolix", "duzizen") else "bf16 (llama: fp16)", "data": "synthetic",
            "steps": args.steps, "warmup": max(3, args.warmup), "sizes": {}}
     for nm in names:
         out["sizes"][nm] = fn(torch, nm, args.steps, args.warmup)

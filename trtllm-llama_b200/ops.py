@@ -785,11 +785,11 @@ def mlstm_gates(proj, col_i, col_f, bias_i, bias_f, cap, m_state, batch, heads):
 FORCE_ROW_SCAN = False      # A/B: the decayed linear attention row by row also for prompt portions
 
 
-def decay_attention_scan(q, k, v, state, batch, heads, dim, vdim, log_ab=None, head_decay=None, ones_col=False):
+def decay_attention_scan(q, k, v, state, batch, heads, dim, vdim, log_ab=None, head_decay=None, ones_col=False, q_scale=1.0):
     """S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t per (sequence, head) over every sequence's rows, from and into ``state``
     (fp32 view [slots, >= heads * vcols * dim], row stride = the slot stride).  q, k fp32 [N, >= heads * dim], v fp32 [N, >= heads *
     vdim] (any row strides).  ``log_ab`` fp32 [N, heads, 2] (ln a, ln b) or ``head_decay`` fp32 [heads] (a fixed, b = 1).
-    ``ones_col``: a further value column of ones (vcols = vdim + 1).  -> fp32 [N, heads, vcols]."""
+    ``ones_col``: a further value column of ones (vcols = vdim + 1).  ``q_scale``: a factor on every query.  -> fp32 [N, heads, vcols]."""
     _chk_dev(q, k, v, state, log_ab, head_decay)
     for t in (q, k, v):
         if t.dtype != torch.float32 or t.stride(1) != 1:
@@ -798,7 +798,7 @@ def decay_attention_scan(q, k, v, state, batch, heads, dim, vdim, log_ab=None, h
     out = torch.empty((q.shape[0], heads, vcols), dtype=torch.float32, device=q.device)
     check(_rl.tb_decay_attention_scan(_p(out), _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(log_ab), _p(head_decay),
                                       _p(state), state.stride(0), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
-                                      _p(batch.seq_slot), q.shape[0], batch.num_seqs, heads, dim, vdim, int(bool(ones_col)),
+                                      _p(batch.seq_slot), q.shape[0], batch.num_seqs, heads, dim, vdim, int(bool(ones_col)), float(q_scale),
                                       1 if FORCE_ROW_SCAN else batch.max_len, _stream()), "tb_decay_attention_scan")
     return out
 
