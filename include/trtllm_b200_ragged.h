@@ -103,10 +103,16 @@ int tb_residual_sandwich_layernorm_rows(float* x, int64_t ldx, const float* y, i
 /* Per-layer token input, one kernel per layer: e = side_embed[ids[n], e_off : e_off + sd] (row stride lde), g = gelu_tanh(w_gate x)
  * * e (w_gate [sd, width]), y = w_proj g (w_proj [width, sd]), x <- x + y / sqrt(mean(y^2) + eps) * norm_w.  The operands of the two
  * products are rounded to the storage type w_dtype; sums, norm and residual are fp32.  With w_pre the next layer's input leaves the
- * same kernel: h = LN(x; w_pre, b_pre), or x / rms(x) * w_pre when pre_rms != 0. */
-int tb_token_side_input(float* x, int64_t ldx, const void* side_embed, int64_t lde, int e_off, const int* ids, int vocab,
-                        const void* w_gate, const void* w_proj, const void* norm_w, int w_dtype, float eps, int rows, int width, int sd,
-                        const void* w_pre, const void* b_pre, int pre_rms, void* h, int h_dtype, int64_t ldh, tb_stream_t stream);
+ * same kernel: h = LN(x; w_pre, b_pre), or x / rms(x) * w_pre when pre_rms != 0.
+ * y_in != NULL (fp32 [rows, width], row stride ldy): y has been computed by the caller — prompt-sized steps run the two products
+ * as projections with tb_side_gate_mul between them — and the kernel does the norm, the residual step and the next norm. */
+int tb_token_side_input(float* x, int64_t ldx, const float* y_in, int64_t ldy, const void* side_embed, int64_t lde, int e_off,
+                        const int* ids, int vocab, const void* w_gate, const void* w_proj, const void* norm_w, int w_dtype, float eps,
+                        int rows, int width, int sd, const void* w_pre, const void* b_pre, int pre_rms, void* h, int h_dtype,
+                        int64_t ldh, tb_stream_t stream);
+/* g[n, j] = gelu_tanh(z[n, j]) * side_embed[ids[n], e_off + j], j < sd, stored as g_dtype [rows, sd] contiguous; z fp32 (row stride ldz). */
+int tb_side_gate_mul(void* g, int g_dtype, const float* z, int64_t ldz, const void* side_embed, int e_dtype, int64_t lde, int e_off,
+                     const int* ids, int vocab, int rows, int sd, tb_stream_t stream);
 /* out fp32 = out_scale * (a / rms(a) * wa + b / rms(b) * wb): two mixers side by side, each RMS-normalised over the row with its
  * own weight (a, b fp32 rows). */
 int tb_rmsnorm_pair_sum(float* out, int64_t ldo, const float* a, int64_t lda, const float* b, int64_t ldb, const void* wa,

@@ -136,11 +136,12 @@ def test_residual_step_between_two_layer_norms(cols):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width,sd,layer,nl", [(40, 3, 1, 4), (64, 16, 0, 1), (300, 1, 2, 3), (1030, 7, 5, 6)])
-def test_token_side_input(dtype, width, sd, layer, nl):
+@pytest.mark.parametrize("n", [5, 45], ids=["one-kernel", "products-as-projections"])
+@pytest.mark.parametrize("width,sd,layer,nl", [(40, 3, 1, 4), (64, 16, 0, 1), (300, 1, 2, 3), (1030, 7, 5, 6), (256, 72, 1, 2)])
+def test_token_side_input(dtype, width, sd, layer, nl, n):
     from trtllm_llama_b200 import ops
     g = torch.Generator().manual_seed(width + sd)
-    vocab, n = 37, 13
+    vocab = 37
     toks = _tokens(n, vocab, 3)
     t = {"side.embed": torch.randn(vocab, nl * sd, generator=g), f"l{layer}.side.gate": torch.randn(sd, width, generator=g) * width ** -0.5,
          f"l{layer}.side.proj": torch.randn(width, sd, generator=g), f"l{layer}.side.norm": torch.randn(width, generator=g) * 0.2 + 0.7}
@@ -207,7 +208,7 @@ def _gates_plain(zi, zf, bi, bf, cap):
 
 
 @pytest.mark.parametrize("cap", [15.0, 2.0, 0.0])
-@pytest.mark.parametrize("cuts", [[200], [1] * 5 + [31, 32, 33, 98], [2, 198]])
+@pytest.mark.parametrize("cuts", [[200], [1] * 5 + [31, 32, 33, 98], [2, 198], [255, 257, 1, 600]])
 def test_matrix_memory_gates_and_running_maximum(cap, cuts):
     from trtllm_llama_b200 import ops
     g = torch.Generator().manual_seed(int(cap) + len(cuts))

@@ -224,7 +224,9 @@ RAGGED_SIGNATURES = {
                                           i32, i32, i32, i32, i32, i32, i32, vp, vp, vp]),
     "tb_embed_bigram": (i32, [vp, vp, vp, i32, vp, vp, f32, i32, i32, i32, i32, i32, i32, vp]),
     "tb_residual_sandwich_layernorm_rows": (i32, [vp, i64, vp, i64, vp, vp, vp, vp, i32, f32, f32, vp, i32, i64, i32, i32, vp]),
-    "tb_token_side_input": (i32, [vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, f32, i32, i32, i32, vp, vp, i32, vp, i32, i64, vp]),
+    "tb_token_side_input": (i32, [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, f32, i32, i32, i32, vp, vp, i32, vp, i32, i64,
+                                  vp]),
+    "tb_side_gate_mul": (i32, [vp, i32, vp, i64, vp, i32, i64, i32, vp, i32, i32, i32, vp]),
     "tb_rmsnorm_pair_sum": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, i32, f32, f32, i32, i32, vp]),
     "tb_decay_attention_scan": (i32, [vp, vp, i64, vp, i64, vp, i64, vp, vp, vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
                                       f32, i32, vp]),

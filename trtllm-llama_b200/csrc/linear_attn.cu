@@ -8,8 +8,8 @@
 // Everything here is fp32: the state, the decays and their logarithms, the products that enter the state.
 //
 //   rope_heads_kernel        a thread per rotated pair: (2i, 2i + 1) or (i, i + dims / 2), with an output factor per head range
-//   mlstm_gates_kernel       a warp per (sequence, head): capped gates, then the running maximum m_t = max(f_t + m_(t-1), i_t) as a
-//                            max-plus prefix scan over 32 rows at a time; emits ln a_t = f_t + m_(t-1) - m_t, ln b_t = i_t - m_t, m_t
+//   mlstm_gates_kernel       a CTA per (sequence, head): capped gates, then the running maximum m_t = max(f_t + m_(t-1), i_t) as a
+//                            max-plus prefix scan over 256 rows at a time; emits ln a_t = f_t + m_(t-1) - m_t, ln b_t = i_t - m_t, m_t
 //   decay_scan_rows_kernel   row by row, a warp per value column with dim over its lanes (generation steps, any dim <= 1024)
 //   decay_scan_chunk_kernel  prompt portions, 32 rows at a time: the chunk's own products A[t, s] = (q_t . k_s) a_(s+1..t) b_s, then
 //                            o = a_(..t) S0^T q_t + A V and S <- a_(..n) S0 + K^T (w V) as register-tiled fp32 products: a thread owns
@@ -67,14 +67,17 @@ struct GateArgs {
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-__global__ void __launch_bounds__(32) mlstm_gates_kernel(float* log_ab, float* m_out, GateArgs a) {
-  const int h = blockIdx.x, e = blockIdx.y, lane = threadIdx.x;
+// one CTA of 8 warps per (sequence, head), 256 rows per trip: a warp scans its 32 rows, the warps' maps meet in shared memory
+__global__ void __launch_bounds__(256) mlstm_gates_kernel(float* log_ab, float* m_out, GateArgs a) {
+  __shared__ float wF[8], wI[8];
+  __shared__ float m_carry;
+  const int h = blockIdx.x, e = blockIdx.y, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int len = a.seq_len[e], start = a.seq_start[e], past = a.seq_past[e];
   float* ms = a.m_state + (int64_t) a.seq_slot[e] * a.m_stride + h;
   float m = past > 0 ? *ms : 0.f;                      // the maximum starts at 0, not at -inf
   const float bi = a.bias_i ? ld_w(a.bias_i, a.w_dtype, h) : 0.f, bf = a.bias_f ? ld_w(a.bias_f, a.w_dtype, h) : 0.f;
-  for (int c0 = 0; c0 < len; c0 += 32) {
-    const int t = c0 + lane;
+  for (int c0 = 0; c0 < len; c0 += 256) {
+    const int t = c0 + threadIdx.x;
     const bool live = t < len;
     float ig = -INFINITY, fg = 0.f;                    // a dead lane is the identity map m -> max(m + 0, -inf)
     if (live) {
@@ -84,25 +87,31 @@ __global__ void __launch_bounds__(32) mlstm_gates_kernel(float* log_ab, float* m
       ig = zi;
       fg = log_sigmoid(zf);
     }
-    // inclusive max-plus scan: lane t ends with the map of rows c0..t in a row, m -> max(m + F, I)
+    // inclusive max-plus scan: lane t ends with the map of its warp's rows up to t in a row, m -> max(m + F, I)
     float F = fg, I = ig;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const float Fp = __shfl_up_sync(0xffffffffu, F, o), Ip = __shfl_up_sync(0xffffffffu, I, o);
       if (lane >= o) { I = fmaxf(Ip + F, I); F = Fp + F; }
     }
-    const float mt = fmaxf(m + F, I);
+    if (lane == 31) { wF[warp] = F; wI[warp] = I; }
+    __syncthreads();
+    float PF = 0.f, PI = -INFINITY;                    // the map of the warps in front of this one
+    for (int w = 0; w < warp; ++w) { PI = fmaxf(PI + wF[w], wI[w]); PF += wF[w]; }
+    const float mt = fmaxf(m + (PF + F), fmaxf(PI + F, I));
     float mp = __shfl_up_sync(0xffffffffu, mt, 1);
-    if (lane == 0) mp = m;
+    if (lane == 0) mp = fmaxf(m + PF, PI);             // the row in front of this warp's first
     if (live) {
       const int64_t o = (int64_t) (start + t) * a.heads + h;
-      log_ab[2 * o] = fminf(fg + mp - mt, 0.f);      // m_t >= f_t + m_(t-1); the scan's sums may round it a few ulp the other way
+      log_ab[2 * o] = fminf(fg + mp - mt, 0.f);        // m_t >= f_t + m_(t-1); the scan's sums may round it a few ulp the other way
       log_ab[2 * o + 1] = ig - mt;
       m_out[o] = mt;
     }
-    m = __shfl_sync(0xffffffffu, mt, 31);
+    if (threadIdx.x == 255) m_carry = mt;
+    __syncthreads();
+    m = m_carry;
   }
-  if (lane == 0) *ms = m;
+  if (threadIdx.x == 0) *ms = m;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -159,18 +168,27 @@ __global__ void __launch_bounds__(kRowWarps * 32) decay_scan_rows_kernel(float* 
 }
 
 // Prompt portions, 32 rows at a time.  CTA = (32 value columns, head, sequence), 8 warps: lane = column, warp = an eighth of
-// dim (DPT elements, dim padded to 8 DPT with zeros).  Shared memory (floats):
-//   Q [32][LD] | K [32][LD] | V [32][32] | A [32][33] | part [8][32][32] | L [32] | lbs [32] | eL [32] | wS [32]      LD = 8 DPT + 4
+// dim (DPT elements, dim padded to 8 DPT with zeros).  The chunk's q, k, v tiles arrive through a two-stage cp.async ring (the next
+// chunk's copies fly while this one is worked on) when the rows are 16-byte aligned, through plain loads otherwise.  Shared memory (floats):
+//   Q [2][32][LD] | K [2][32][LD] | V [2][32][32] | A [32][33] | part [8][32][32] | L [32] | lbs [32] | eL [32] | wS [32]      LD = 8 DPT + 4
 constexpr int kChunk = 32;
 
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const uint32_t d = (uint32_t) __cvta_generic_to_shared(dst);
+  const int n = valid ? 16 : 0;                       // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;"); }
+
 template <int DPT>
-__global__ void __launch_bounds__(256) decay_scan_chunk_kernel(float* out, ScanArgs a) {
+__global__ void __launch_bounds__(256) decay_scan_chunk_kernel(float* out, ScanArgs a, int vec) {
   constexpr int DP = 8 * DPT, LD = DP + 4;
   extern __shared__ __align__(16) float sm[];
-  float* Qs = sm;
-  float* Ks = Qs + kChunk * LD;
-  float* Vs = Ks + kChunk * LD;
-  float* As = Vs + kChunk * 32;
+  float* Qs = sm;                                       // [2][kChunk][LD]
+  float* Ks = Qs + 2 * kChunk * LD;
+  float* Vs = Ks + 2 * kChunk * LD;                     // [2][kChunk][32]
+  float* As = Vs + 2 * kChunk * 32;
   float* part = As + kChunk * 33;
   float* Ls = part + 8 * kChunk * 32;
   float* lbs = Ls + kChunk;
@@ -181,6 +199,7 @@ __global__ void __launch_bounds__(256) decay_scan_chunk_kernel(float* out, ScanA
   const int len = a.seq_len[e], start = a.seq_start[e], past = a.seq_past[e];
   const int col = cg * 32 + lane;
   const bool col_ok = col < a.vcols;
+  const bool ones_here = col_ok && col >= a.vdim;       // the column of ones: its value is 1 at every live row
   float* sp = a.state + (int64_t) a.seq_slot[e] * a.state_stride + ((int64_t) h * a.vcols + (col_ok ? col : 0)) * a.dim;
   float s[DPT];
 #pragma unroll
@@ -189,22 +208,51 @@ __global__ void __launch_bounds__(256) decay_scan_chunk_kernel(float* out, ScanA
     s[i] = past > 0 && col_ok && d < a.dim ? sp[d] : 0.f;
   }
   const float fixed_la = a.log_ab ? 0.f : logf(a.head_decay[h]);
-  for (int c0 = 0; c0 < len; c0 += kChunk) {
+
+  auto load_chunk = [&](int c0, int buf) {
     const int n = min(kChunk, len - c0);
     const int64_t row0 = start + c0;
-    __syncthreads();                                   // the previous chunk's tiles have been consumed
-    for (int idx = threadIdx.x; idx < kChunk * DP; idx += 256) {
-      const int t = idx / DP, d = idx % DP;
-      const bool ok = t < n && d < a.dim;
-      Qs[t * LD + d] = ok ? a.q[(row0 + t) * a.ldq + (int64_t) h * a.dim + d] * a.q_scale : 0.f;
-      Ks[t * LD + d] = ok ? a.k[(row0 + t) * a.ldk + (int64_t) h * a.dim + d] : 0.f;
+    float* Qb = Qs + buf * kChunk * LD;
+    float* Kb = Ks + buf * kChunk * LD;
+    float* Vb = Vs + buf * kChunk * 32;
+    if (vec) {
+      for (int idx = threadIdx.x; idx < kChunk * (DP / 4); idx += 256) {
+        const int t = idx / (DP / 4), d = (idx % (DP / 4)) * 4;
+        const bool ok = t < n && d < a.dim;            // dim is a multiple of 4 here: the four elements are in or out together
+        cp_async16(Qb + t * LD + d, ok ? a.q + (row0 + t) * a.ldq + (int64_t) h * a.dim + d : a.q, ok);
+        cp_async16(Kb + t * LD + d, ok ? a.k + (row0 + t) * a.ldk + (int64_t) h * a.dim + d : a.k, ok);
+      }
+      {
+        const int t = threadIdx.x / 8, c = cg * 32 + (threadIdx.x % 8) * 4;
+        const bool ok = t < n && c < a.vdim;
+        cp_async16(Vb + t * 32 + (threadIdx.x % 8) * 4, ok ? a.v + (row0 + t) * a.ldv + (int64_t) h * a.vdim + c : a.v, ok);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < kChunk * DP; idx += 256) {
+        const int t = idx / DP, d = idx % DP;
+        const bool ok = t < n && d < a.dim;
+        Qb[t * LD + d] = ok ? a.q[(row0 + t) * a.ldq + (int64_t) h * a.dim + d] : 0.f;
+        Kb[t * LD + d] = ok ? a.k[(row0 + t) * a.ldk + (int64_t) h * a.dim + d] : 0.f;
+      }
+      for (int idx = threadIdx.x; idx < kChunk * 32; idx += 256) {
+        const int t = idx / 32, c = cg * 32 + idx % 32;
+        Vb[idx] = t < n && c < a.vdim ? a.v[(row0 + t) * a.ldv + (int64_t) h * a.vdim + c] : 0.f;
+      }
     }
-    for (int idx = threadIdx.x; idx < kChunk * 32; idx += 256) {
-      const int t = idx / 32, c = cg * 32 + idx % 32;
-      float v = 0.f;
-      if (t < n && c < a.vcols) v = c < a.vdim ? a.v[(row0 + t) * a.ldv + (int64_t) h * a.vdim + c] : 1.f;
-      Vs[idx] = v;
-    }
+    cp_async_commit();
+  };
+
+  load_chunk(0, 0);
+  int buf = 0;
+  for (int c0 = 0; c0 < len; c0 += kChunk, buf ^= 1) {
+    const int n = min(kChunk, len - c0);
+    const int64_t row0 = start + c0;
+    const float* Qb = Qs + buf * kChunk * LD;
+    const float* Kb = Ks + buf * kChunk * LD;
+    const float* Vb = Vs + buf * kChunk * 32;
+    cp_async_wait_all();
+    __syncthreads();                                   // this chunk's tiles have landed; the other stage and part / A are free
+    if (c0 + kChunk < len) load_chunk(c0 + kChunk, buf ^ 1);
     if (warp == 0) {
       float la = 0.f, lb = -INFINITY;
       if (lane < n) {
@@ -227,13 +275,13 @@ __global__ void __launch_bounds__(256) decay_scan_chunk_kernel(float* out, ScanA
     // the chunk's own products: thread -> rows t = warp * 4 + j, key s = lane
     {
       float dot[4] = {0.f, 0.f, 0.f, 0.f};
-      const float* kr = Ks + lane * LD;
+      const float* kr = Kb + lane * LD;
 #pragma unroll 4
       for (int d = 0; d < DP; d += 4) {
         const float4 kv = *reinterpret_cast<const float4*>(kr + d);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float4 qv = *reinterpret_cast<const float4*>(Qs + (warp * 4 + j) * LD + d);
+          const float4 qv = *reinterpret_cast<const float4*>(Qb + (warp * 4 + j) * LD + d);
           dot[j] = fmaf(qv.x, kv.x, dot[j]);
           dot[j] = fmaf(qv.y, kv.y, dot[j]);
           dot[j] = fmaf(qv.z, kv.z, dot[j]);
@@ -243,32 +291,38 @@ __global__ void __launch_bounds__(256) decay_scan_chunk_kernel(float* out, ScanA
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int t = warp * 4 + j;
-        As[t * 33 + lane] = (lane <= t && t < n) ? dot[j] * expf(Ls[t] + lbs[lane]) : 0.f;
+        As[t * 33 + lane] = (lane <= t && t < n) ? dot[j] * a.q_scale * expf(Ls[t] + lbs[lane]) : 0.f;
       }
     }
     __syncthreads();
+    // read-out against the carried state: 32 independent sums per thread, the state's elements outermost
     float acc[kChunk];
 #pragma unroll
-    for (int t = 0; t < kChunk; ++t) {
-      float p = 0.f;
-      const float* qr = Qs + t * LD + warp * DPT;
-      if constexpr (DPT % 4 == 0) {
+    for (int t = 0; t < kChunk; ++t) acc[t] = 0.f;
+    if constexpr (DPT % 4 == 0) {
 #pragma unroll
-        for (int i = 0; i < DPT; i += 4) {
-          const float4 qv = *reinterpret_cast<const float4*>(qr + i);
-          p = fmaf(s[i], qv.x, p); p = fmaf(s[i + 1], qv.y, p); p = fmaf(s[i + 2], qv.z, p); p = fmaf(s[i + 3], qv.w, p);
-        }
-      } else {
+      for (int i = 0; i < DPT; i += 4) {
 #pragma unroll
-        for (int i = 0; i < DPT; i += 2) {
-          const float2 qv = *reinterpret_cast<const float2*>(qr + i);
-          p = fmaf(s[i], qv.x, p); p = fmaf(s[i + 1], qv.y, p);
+        for (int t = 0; t < kChunk; ++t) {
+          const float4 qv = *reinterpret_cast<const float4*>(Qb + t * LD + warp * DPT + i);
+          acc[t] = fmaf(s[i], qv.x, acc[t]); acc[t] = fmaf(s[i + 1], qv.y, acc[t]);
+          acc[t] = fmaf(s[i + 2], qv.z, acc[t]); acc[t] = fmaf(s[i + 3], qv.w, acc[t]);
         }
       }
-      acc[t] = p * eL[t];
+    } else {
+#pragma unroll
+      for (int i = 0; i < DPT; i += 2) {
+#pragma unroll
+        for (int t = 0; t < kChunk; ++t) {
+          const float2 qv = *reinterpret_cast<const float2*>(Qb + t * LD + warp * DPT + i);
+          acc[t] = fmaf(s[i], qv.x, acc[t]); acc[t] = fmaf(s[i + 1], qv.y, acc[t]);
+        }
+      }
     }
+#pragma unroll
+    for (int t = 0; t < kChunk; ++t) acc[t] *= eL[t] * a.q_scale;
     for (int sk = warp; sk < n; sk += 8) {             // this warp's share of the chunk's keys
-      const float vv = Vs[sk * 32 + lane];
+      const float vv = ones_here ? 1.f : Vb[sk * 32 + lane];
 #pragma unroll
       for (int t = 0; t < kChunk; ++t) acc[t] = fmaf(As[t * 33 + sk], vv, acc[t]);
     }
@@ -279,8 +333,8 @@ __global__ void __launch_bounds__(256) decay_scan_chunk_kernel(float* out, ScanA
 #pragma unroll
     for (int i = 0; i < DPT; ++i) s[i] *= dec;
     for (int sk = 0; sk < n; ++sk) {
-      const float wv = wS[sk] * Vs[sk * 32 + lane];
-      const float* kr = Ks + sk * LD + warp * DPT;
+      const float wv = wS[sk] * (ones_here ? 1.f : Vb[sk * 32 + lane]);
+      const float* kr = Kb + sk * LD + warp * DPT;
       if constexpr (DPT % 4 == 0) {
 #pragma unroll
         for (int i = 0; i < DPT; i += 4) {
@@ -317,14 +371,17 @@ __global__ void __launch_bounds__(256) decay_scan_chunk_kernel(float* out, ScanA
 template <int DPT>
 int launch_chunk(float* out, const ScanArgs& a, int seqs, cudaStream_t st) {
   constexpr int DP = 8 * DPT, LD = DP + 4;
-  constexpr size_t smem = ((size_t) 2 * kChunk * LD + kChunk * 32 + kChunk * 33 + 8 * kChunk * 32 + 4 * kChunk) * sizeof(float);
+  constexpr size_t smem = ((size_t) 4 * kChunk * LD + 2 * kChunk * 32 + kChunk * 33 + 8 * kChunk * 32 + 4 * kChunk) * sizeof(float);
   static bool raised = false;
   if (!raised && smem > 48 * 1024) {
     TB_CHECK_CUDA(cudaFuncSetAttribute(decay_scan_chunk_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     raised = true;
   }
+  // cp.async moves 16 bytes: every row of q, k, v and every head and column group inside it must start on such a boundary
+  const int vec = a.dim % 4 == 0 && a.vdim % 4 == 0 && a.ldq % 4 == 0 && a.ldk % 4 == 0 && a.ldv % 4 == 0 &&
+                  (uintptr_t) a.q % 16 == 0 && (uintptr_t) a.k % 16 == 0 && (uintptr_t) a.v % 16 == 0;
   dim3 grid((a.vcols + 31) / 32, a.heads, seqs);
-  decay_scan_chunk_kernel<DPT><<<grid, 256, smem, st>>>(out, a);
+  decay_scan_chunk_kernel<DPT><<<grid, 256, smem, st>>>(out, a, vec);
   return 0;
 }
 
@@ -397,7 +454,7 @@ extern "C" int tb_mlstm_gates(float* log_ab, float* m_out, const float* proj, in
   if ((bias_i || bias_f) && w_dtype != TB_DT_F32 && w_dtype != TB_DT_BF16) return -1;
   if (seqs == 0) return 0;
   GateArgs a{proj, ldp, col_i, col_f, bias_i, bias_f, w_dtype, cap, m_state, m_stride, seq_start, seq_len, seq_past, seq_slot, heads};
-  mlstm_gates_kernel<<<dim3(heads, seqs), 32, 0, (cudaStream_t) stream>>>(log_ab, m_out, a);
+  mlstm_gates_kernel<<<dim3(heads, seqs), 256, 0, (cudaStream_t) stream>>>(log_ab, m_out, a);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

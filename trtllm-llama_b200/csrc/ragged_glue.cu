@@ -257,7 +257,9 @@ __global__ void __launch_bounds__(256) residual_sandwich_layernorm_kernel(float*
 // y = W_proj g; x <- x + y / rms(y) * norm_w; then, when w_pre is given, h = LN(x; w_pre, b_pre) or the RMS norm (b_pre NULL and
 // pre_rms) of the NEXT layer.  Operands of the two products are rounded to the storage type (w_dtype) as a projection kernel
 // would; sums, the norm and the residual are fp32.  Shared memory: x row [width] | g [sd] | y [width].
+// y_in != NULL: the two products have been run as projections (prompt-sized steps) and y is read from there.
 struct SideArgs {
+  const float* y_in; int64_t ldy;
   float* x; int64_t ldx;
   const void* side_embed; int64_t lde; int e_off;
   const int* ids; int vocab;
@@ -277,23 +279,33 @@ __global__ void __launch_bounds__(256) token_side_input_kernel(SideArgs a) {
   float* ys = gs + a.sd;
   const int row = blockIdx.x, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   float* xr = a.x + (int64_t) row * a.ldx;
-  for (int c = threadIdx.x; c < a.width; c += 256) xs[c] = round_like(xr[c], a.w_dtype);
-  __syncthreads();
-  int id = a.ids[row];
-  id = id < 0 ? 0 : (id >= a.vocab ? a.vocab - 1 : id);
-  for (int j = warp; j < a.sd; j += 8) {
-    float acc = 0.f;
-    for (int c = lane; c < a.width; c += 32) acc = fmaf(ld_f(a.w_gate, a.w_dtype, (int64_t) j * a.width + c), xs[c], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) gs[j] = round_like(gelu_tanh_f(acc) * ld_f(a.side_embed, a.w_dtype, (int64_t) id * a.lde + a.e_off + j), a.w_dtype);
-  }
-  __syncthreads();
   float ss = 0.f;
-  for (int c = threadIdx.x; c < a.width; c += 256) {
-    float acc = 0.f;
-    for (int j = 0; j < a.sd; ++j) acc = fmaf(ld_f(a.w_proj, a.w_dtype, (int64_t) c * a.sd + j), gs[j], acc);
-    ys[c] = acc;
-    ss = fmaf(acc, acc, ss);
+  if (a.y_in) {
+    const float* yr = a.y_in + (int64_t) row * a.ldy;
+    for (int c = threadIdx.x; c < a.width; c += 256) { const float v = yr[c]; ys[c] = v; ss = fmaf(v, v, ss); }
+  } else {
+    for (int c = threadIdx.x; c < a.width; c += 256) xs[c] = round_like(xr[c], a.w_dtype);
+    __syncthreads();
+    int id = a.ids[row];
+    id = id < 0 ? 0 : (id >= a.vocab ? a.vocab - 1 : id);
+    for (int j = warp; j < a.sd; j += 8) {
+      float acc = 0.f;
+      for (int c = lane; c < a.width; c += 32) acc = fmaf(ld_f(a.w_gate, a.w_dtype, (int64_t) j * a.width + c), xs[c], acc);
+      acc = warp_sum(acc);
+      if (lane == 0) gs[j] = round_like(gelu_tanh_f(acc) * ld_f(a.side_embed, a.w_dtype, (int64_t) id * a.lde + a.e_off + j), a.w_dtype);
+    }
+    __syncthreads();
+    // a warp per output column, the column's sd weights (contiguous) over its lanes; every thread of the warp keeps the sum of
+    // squares of the warp's columns, so the block sum below counts each column 32 times: divided out
+    for (int c = warp; c < a.width; c += 8) {
+      float acc = 0.f;
+      for (int j = lane; j < a.sd; j += 32) acc = fmaf(ld_f(a.w_proj, a.w_dtype, (int64_t) c * a.sd + j), gs[j], acc);
+      acc = warp_sum(acc);
+      if (lane == 0) ys[c] = acc;
+      ss = fmaf(acc, acc, ss);
+    }
+    ss *= 1.f / 32.f;
+    __syncthreads();
   }
   const float inv_y = 1.f / sqrtf(block_sum_256(ss, red, &bc) / (float) a.width + a.eps);
   float s = 0.f, s2 = 0.f;
@@ -318,6 +330,19 @@ __global__ void __launch_bounds__(256) token_side_input_kernel(SideArgs a) {
     float v = (ys[c] - mean) * inv * ld_f(a.w_pre, a.w_dtype, c);
     if (a.b_pre) v += ld_f(a.b_pre, a.w_dtype, c);
     st_f(a.h, a.h_dtype, (int64_t) row * a.ldh + c, v);
+  }
+}
+
+// g[n, j] = gelu_tanh(z[n, j]) * side_embed[ids[n], e_off + j] in g's type: between the two projections of the per-layer token
+// input when they run as prompt-sized products
+__global__ void side_gate_mul_kernel(void* g, int g_dtype, const float* z, int64_t ldz, const void* side_embed, int e_dtype, int64_t lde,
+                                     int e_off, const int* ids, int vocab, int sd, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
+    const int64_t row = i / sd;
+    const int j = (int) (i % sd);
+    int id = ids[row];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    st_f(g, g_dtype, i, gelu_tanh_f(z[row * ldz + j]) * ld_f(side_embed, e_dtype, (int64_t) id * lde + e_off + j));
   }
 }
 
@@ -509,13 +534,12 @@ extern "C" int tb_residual_sandwich_layernorm_rows(float* x, int64_t ldx, const 
   return 0;
 }
 
-extern "C" int tb_token_side_input(float* x, int64_t ldx, const void* side_embed, int64_t lde, int e_off, const int* ids, int vocab,
-                                   const void* w_gate, const void* w_proj, const void* norm_w, int w_dtype, float eps, int rows,
-                                   int width, int sd, const void* w_pre, const void* b_pre, int pre_rms, void* h, int h_dtype,
-                                   int64_t ldh, tb_stream_t stream) {
-  if (!x || !side_embed || !ids || !w_gate || !w_proj || !norm_w || !dt_ok(w_dtype) || width <= 0 || sd <= 0 || rows < 0 ||
-      vocab <= 0 || e_off < 0)
-    return -1;
+extern "C" int tb_token_side_input(float* x, int64_t ldx, const float* y_in, int64_t ldy, const void* side_embed, int64_t lde, int e_off,
+                                   const int* ids, int vocab, const void* w_gate, const void* w_proj, const void* norm_w, int w_dtype,
+                                   float eps, int rows, int width, int sd, const void* w_pre, const void* b_pre, int pre_rms, void* h,
+                                   int h_dtype, int64_t ldh, tb_stream_t stream) {
+  if (!x || !norm_w || !dt_ok(w_dtype) || width <= 0 || sd <= 0 || rows < 0 || vocab <= 0 || e_off < 0) return -1;
+  if (!y_in && (!side_embed || !ids || !w_gate || !w_proj)) return -1;
   if (w_pre && (!h || !dt_ok(h_dtype))) return -1;
   const size_t smem = ((size_t) 2 * width + sd) * sizeof(float);
   if (smem > 200 * 1024) return -2;
@@ -525,9 +549,20 @@ extern "C" int tb_token_side_input(float* x, int64_t ldx, const void* side_embed
     TB_CHECK_CUDA(cudaFuncSetAttribute(token_side_input_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     raised = smem;
   }
-  SideArgs a{x, ldx, side_embed, lde, e_off, ids, vocab, w_gate, w_proj, norm_w, w_dtype, eps, width, sd, w_pre, b_pre, pre_rms, h,
-             h_dtype, ldh};
+  SideArgs a{y_in, ldy, x, ldx, side_embed, lde, e_off, ids, vocab, w_gate, w_proj, norm_w, w_dtype, eps, width, sd, w_pre, b_pre,
+             pre_rms, h, h_dtype, ldh};
   token_side_input_kernel<<<rows, 256, smem, (cudaStream_t) stream>>>(a);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_side_gate_mul(void* g, int g_dtype, const float* z, int64_t ldz, const void* side_embed, int e_dtype, int64_t lde,
+                                int e_off, const int* ids, int vocab, int rows, int sd, tb_stream_t stream) {
+  if (!g || !z || !side_embed || !ids || !dt_ok(g_dtype) || !dt_ok(e_dtype) || rows < 0 || sd <= 0 || vocab <= 0 || e_off < 0) return -1;
+  if (rows == 0) return 0;
+  const int64_t n = (int64_t) rows * sd;
+  const int grid = (int) ((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  side_gate_mul_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(g, g_dtype, z, ldz, side_embed, e_dtype, lde, e_off, ids, vocab, sd, n);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

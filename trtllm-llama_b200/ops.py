@@ -835,6 +835,9 @@ def residual_sandwich_layernorm_rows(x, y, w_post, b_post, out_scale, eps, w_pre
     return h
 
 
+SIDE_FUSED_MAX_ROWS = 8     # up to this many rows the per-layer token input is one kernel; above, its products run as projections
+
+
 def token_side_input(x, side_embed, e_off, ids, w_gate, w_proj, norm_w, eps, w_pre=None, b_pre=None, pre_rms=False,
                      out_dtype=torch.float32):
     """x += rms_norm(w_proj (gelu_tanh(w_gate x) * side_embed[ids, e_off : e_off + sd])) * norm_w in place (sd = w_gate.shape[0]);
@@ -848,10 +851,18 @@ def token_side_input(x, side_embed, e_off, ids, w_gate, w_proj, norm_w, eps, w_p
         if t is not None and t.dtype != w_gate.dtype:
             raise TypeError("token_side_input: tensors of one storage type")
     h = torch.empty(x.shape, dtype=out_dtype, device=x.device) if w_pre is not None else None
-    check(_rl.tb_token_side_input(_p(x), x.stride(0), _p(side_embed), side_embed.stride(0), int(e_off), _p(ids), side_embed.shape[0],
-                                  _p(w_gate), _p(w_proj), _p(norm_w), _dt(w_gate), float(eps), x.shape[0], width, sd, _p(w_pre), _p(b_pre),
-                                  int(bool(pre_rms)), _p(h), _dt(h) if h is not None else 0, h.stride(0) if h is not None else 0,
-                                  _stream()), "tb_token_side_input")
+    y = None
+    if x.shape[0] > SIDE_FUSED_MAX_ROWS:
+        # prompt-sized steps: the two products as projections (tensor cores for bf16), the kernel below finishes
+        z = linear(x, w_gate, out_dtype=torch.float32)
+        g = torch.empty((x.shape[0], sd), dtype=w_gate.dtype, device=x.device)
+        check(_rl.tb_side_gate_mul(_p(g), _dt(g), _p(z), z.stride(0), _p(side_embed), _dt(side_embed), side_embed.stride(0), int(e_off),
+                                   _p(ids), side_embed.shape[0], x.shape[0], sd, _stream()), "tb_side_gate_mul")
+        y = linear(g, w_proj, out_dtype=torch.float32)
+    check(_rl.tb_token_side_input(_p(x), x.stride(0), _p(y), y.stride(0) if y is not None else 0, _p(side_embed), side_embed.stride(0),
+                                  int(e_off), _p(ids), side_embed.shape[0], _p(w_gate), _p(w_proj), _p(norm_w), _dt(w_gate), float(eps),
+                                  x.shape[0], width, sd, _p(w_pre), _p(b_pre), int(bool(pre_rms)), _p(h), _dt(h) if h is not None else 0,
+                                  h.stride(0) if h is not None else 0, _stream()), "tb_token_side_input")
     return h
 
 
