@@ -312,12 +312,18 @@ int tb_gated_rmsnorm_heads(void* out, int dtype, const float* o, const float* ga
  * state: slot s at state + s * state_stride, [heads, vcols, dim] (a column's dim elements contiguous); zeros at a sequence's
  * first position.  q_scale: a factor on every query (1: none).  out fp32 [N, heads, vcols].  max_len: the longest seq_len
  * (host): from 4 rows on (dim <= 256) the rows are
- * resolved 32 at a time from the portion's first row (the same recurrence up to fp32 rounding), else row by row. */
+ * resolved 32 at a time from the portion's first row (the same recurrence up to fp32 rounding), else row by row.
+ * segments > 1 with workspace (fp32, seqs * segments * (heads * vcols * dim + heads) values, 16-byte aligned): a
+ * long portion is cut into that many segments (whole blocks of 32 rows) that run side by side — every segment's own end state
+ * from zero, the states carried from segment to segment in order, then every segment from its carried state.
+ * tb_decay_scan_segments tells how many segments fill the chip (1: none). */
 int tb_decay_attention_scan(float* out, const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
                             const float* log_ab, const float* head_decay, float* state, int64_t state_stride, const int* seq_start,
                             const int* seq_len, const int* seq_past, const int* seq_slot, int rows, int seqs, int heads, int dim,
-                            int vdim, int ones_col, float q_scale, int max_len, tb_stream_t stream);
-/* A/B switch for tests and measurements: 1 keeps tb_decay_attention_scan row by row; 0: by max_len (default). */
+                            int vdim, int ones_col, float q_scale, int max_len, float* workspace, int segments, tb_stream_t stream);
+int tb_decay_scan_segments(int seqs, int heads, int vcols, int max_len);
+/* A/B switch for tests and measurements: 1 keeps tb_decay_attention_scan row by row; 2 keeps long portions in one segment; 0: by
+ * max_len (default). */
 int tb_decay_scan_set_mode(int mode);
 /* Gates of an mLSTM matrix memory.  Per row and head, from proj (fp32, row stride ldp): i = cap * tanh((proj[col_i + h] + bias_i[h])
  * / cap), f = logsigmoid(cap * tanh((proj[col_f + h] + bias_f[h]) / cap)) (cap <= 0: no cap); running maximum m_t = max(f_t +

@@ -137,7 +137,7 @@ def test_residual_step_between_two_layer_norms(cols):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n", [5, 45], ids=["one-kernel", "products-as-projections"])
-@pytest.mark.parametrize("width,sd,layer,nl", [(40, 3, 1, 4), (64, 16, 0, 1), (300, 1, 2, 3), (1030, 7, 5, 6), (256, 72, 1, 2)])
+@pytest.mark.parametrize("width,sd,layer,nl", [(40, 3, 1, 4), (64, 16, 0, 1), (300, 1, 2, 3), (1030, 7, 5, 6), (256, 72, 1, 2), (512, 16, 0, 2)])
 def test_token_side_input(dtype, width, sd, layer, nl, n):
     from trtllm_llama_b200 import ops
     g = torch.Generator().manual_seed(width + sd)
@@ -277,6 +277,39 @@ def test_decayed_linear_attention_remembers_far_tokens(H, d, dv, ones, cuts, row
     assert (state[[0, 2]] == -7.0).all() and (state[1, H * vc * d:] == -7.0).all(), "neighbouring slots and columns are untouched"
     far = _scan_plain(q.double()[6:], k.double()[6:], vv.double()[6:], la.double()[6:], lb.double()[6:])[0]
     assert (want[-1] - far[-1]).abs().max() > 0.1 * want[-1].abs().max(), "the test's early rows must matter at the end"
+
+
+@pytest.mark.parametrize("H,d,dv,ones", [(2, 16, 12, True), (1, 64, 70, False), (3, 48, 48, True)])
+@pytest.mark.parametrize("lens,pasts", [([900], [0]), ([700, 130, 1, 64], [0, 40, 7, 0]), ([128, 129], [5, 0])])
+def test_long_portions_run_as_segments_side_by_side(H, d, dv, ones, lens, pasts):
+    """Portions long enough to be cut into segments (each segment's own end state, the carry in order, then every segment from its
+    carried state) beside short ones in one batch, sequences that start from a state in their slot and sequences that start from
+    zero: the read-out and the state left behind are the row-by-row recurrence's."""
+    from trtllm_llama_b200 import ops
+    g = torch.Generator().manual_seed(sum(lens) + d)
+    vc = dv + (1 if ones else 0)
+    assert ops._rl.tb_decay_scan_segments(len(lens), H, vc, max(lens)) > 1
+    N = sum(lens)
+    q, k, v = torch.randn(N, H, d, generator=g) * d ** -0.5, torch.randn(N, H, d, generator=g), torch.randn(N, H, dv, generator=g)
+    la, lb = -torch.rand(N, H, generator=g) * 0.02, -torch.rand(N, H, generator=g)
+    state0 = torch.randn(len(lens) + 1, H * vc * d + 3, generator=g)
+    state = state0.clone().cuda()
+    b = _batch(lens, pasts, list(range(1, len(lens) + 1)))
+    out = ops.decay_attention_scan(q.reshape(N, -1).cuda(), k.reshape(N, -1).cuda(), v.reshape(N, -1).cuda(), state, b, H, d, dv,
+                                   log_ab=torch.stack([la, lb], dim=-1).cuda(), ones_col=ones)
+    at = 0
+    for i, n in enumerate(lens):
+        S = state0[i + 1, :H * vc * d].double().view(H, vc, d).transpose(1, 2).clone() if pasts[i] else torch.zeros(H, d, vc, dtype=torch.float64)
+        vv = torch.cat([v[at:at + n], torch.ones(n, H, 1)], dim=2) if ones else v[at:at + n]
+        want = torch.zeros(n, H, vc, dtype=torch.float64)
+        for t in range(n):
+            for h in range(H):
+                S[h] = math.exp(la[at + t, h]) * S[h] + math.exp(lb[at + t, h]) * torch.outer(k[at + t, h].double(), vv[t, h].double())
+                want[t, h] = S[h].T @ q[at + t, h].double()
+        _close(out[at:at + n], want, torch.float32, f"read-out of sequence {i}", scale=2.0)
+        _close(state[i + 1, :H * vc * d].view(H, vc, d), S.transpose(1, 2), torch.float32, f"state of sequence {i}", scale=2.0)
+        at += n
+    assert torch.equal(state[0].cpu(), state0[0]) and torch.equal(state[1:, H * vc * d:].cpu(), state0[1:, H * vc * d:])
 
 
 @pytest.mark.parametrize("cuts", [[150], [70, 1, 1, 78]])

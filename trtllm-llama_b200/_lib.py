@@ -229,7 +229,8 @@ RAGGED_SIGNATURES = {
     "tb_side_gate_mul": (i32, [vp, i32, vp, i64, vp, i32, i64, i32, vp, i32, i32, i32, vp]),
     "tb_rmsnorm_pair_sum": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, i32, f32, f32, i32, i32, vp]),
     "tb_decay_attention_scan": (i32, [vp, vp, i64, vp, i64, vp, i64, vp, vp, vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
-                                      f32, i32, vp]),
+                                      f32, i32, vp, i32, vp]),
+    "tb_decay_scan_segments": (i32, [i32, i32, i32, i32]),
     "tb_decay_scan_set_mode": (i32, [i32]),
     "tb_mlstm_gates": (i32, [vp, vp, vp, i64, i32, i32, vp, vp, i32, f32, vp, i64, vp, vp, vp, vp, i32, i32, vp]),
     "tb_rope_heads": (i32, [vp, i64, vp, i64, vp, i32, i32, i32, i32, i32, i32, f32, f32, vp]),

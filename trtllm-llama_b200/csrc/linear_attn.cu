@@ -123,6 +123,11 @@ struct ScanArgs {
   const int *seq_start, *seq_len, *seq_past, *seq_slot;
   int heads, dim, vdim, vcols;                        // vcols = vdim + 1 when a column of ones follows the values
   float q_scale;                                      // every query is multiplied by it as it is read
+  // long portions are cut into segments of seg_rows rows (a multiple of 32) that run side by side: ws [seqs, max_segs, heads, vcols,
+  // dim] holds at index sg + 1 segment sg's own end state from zero and then, after the carry kernel, at index sg the state segment
+  // sg starts from (index 0: a copy of the slot's — the last segment overwrites the slot while the first may still be reading);
+  // lseg [seqs, max_segs, heads] the sum of ln a over the segment.  ws NULL: one segment.
+  float* ws; float* lseg; int max_segs, seg_rows;
 };
 
 constexpr int kRowWarps = 4;
@@ -195,17 +200,26 @@ __global__ void __launch_bounds__(256) decay_scan_chunk_kernel(float* out, ScanA
   float* eL = lbs + kChunk;
   float* wS = eL + kChunk;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int cg = blockIdx.x, h = blockIdx.y, e = blockIdx.z;
-  const int len = a.seq_len[e], start = a.seq_start[e], past = a.seq_past[e];
+  const int cg = blockIdx.x, h = blockIdx.y;
+  const int e = a.ws ? blockIdx.z / a.max_segs : blockIdx.z, sg = a.ws ? blockIdx.z % a.max_segs : 0;
+  const int len_all = a.seq_len[e], past = a.seq_past[e];
+  const int r0 = sg * a.seg_rows;                       // this CTA's rows of the portion: [r0, r1)
+  if (r0 >= len_all) return;
+  const int r1 = a.ws ? min(len_all, r0 + a.seg_rows) : len_all;
+  const int len = r1 - r0, start = a.seq_start[e] + r0;
   const int col = cg * 32 + lane;
   const bool col_ok = col < a.vcols;
   const bool ones_here = col_ok && col >= a.vdim;       // the column of ones: its value is 1 at every live row
   float* sp = a.state + (int64_t) a.seq_slot[e] * a.state_stride + ((int64_t) h * a.vcols + (col_ok ? col : 0)) * a.dim;
+  // the state in front of the first row: the slot's (zeros at a sequence's start), or what the carry kernel left for this segment
+  const bool cut = a.ws && len_all > a.seg_rows;         // this sequence runs as several segments
+  const float* s0 = cut ? a.ws + (((int64_t) e * a.max_segs + sg) * a.heads + h) * a.vcols * a.dim + (int64_t) (col_ok ? col : 0) * a.dim
+                        : (past > 0 ? sp : nullptr);
   float s[DPT];
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
     const int d = warp * DPT + i;
-    s[i] = past > 0 && col_ok && d < a.dim ? sp[d] : 0.f;
+    s[i] = s0 && col_ok && d < a.dim ? s0[d] : 0.f;
   }
   const float fixed_la = a.log_ab ? 0.f : logf(a.head_decay[h]);
 
@@ -359,12 +373,141 @@ __global__ void __launch_bounds__(256) decay_scan_chunk_kernel(float* out, ScanA
       out[((row0 + t) * a.heads + h) * a.vcols + cg * 32 + c] = o;
     }
   }
-  if (col_ok) {
+  if (col_ok && r1 == len_all) {                       // the portion's last rows: the sequence's state
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
       const int d = warp * DPT + i;
       if (d < a.dim) sp[d] = s[i];
     }
+  }
+}
+
+// A segment's own end state, from zero: S <- a_(..n) S + K^T (w V) chunk by chunk, nothing read out.  Same CTA shape and ring as above
+// (keys and values only).  Shared memory (floats): K [2][32][LD] | V [2][32][32] | wS [32] | dec
+template <int DPT>
+__global__ void __launch_bounds__(256) decay_segment_state_kernel(ScanArgs a, int vec) {
+  constexpr int DP = 8 * DPT, LD = DP + 4;
+  extern __shared__ __align__(16) float sm[];
+  float* Ks = sm;
+  float* Vs = Ks + 2 * kChunk * LD;
+  float* wS = Vs + 2 * kChunk * 32;
+  float* dec_s = wS + kChunk;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int cg = blockIdx.x, h = blockIdx.y, e = blockIdx.z / a.max_segs, sg = blockIdx.z % a.max_segs;
+  const int len_all = a.seq_len[e];
+  const int r0 = sg * a.seg_rows;
+  if (r0 + a.seg_rows >= len_all) return;                // the last segment's end state is the sequence's: the main kernel writes it
+  const int start = a.seq_start[e] + r0, len = a.seg_rows;   // whole chunks: seg_rows is a multiple of 32
+  const int col = cg * 32 + lane;
+  const bool col_ok = col < a.vcols;
+  const bool ones_here = col_ok && col >= a.vdim;
+  float s[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) s[i] = 0.f;
+  const float fixed_la = a.log_ab ? 0.f : logf(a.head_decay[h]);
+  float Lsum = 0.f;
+
+  auto load_chunk = [&](int c0, int buf) {
+    const int64_t row0 = start + c0;
+    float* Kb = Ks + buf * kChunk * LD;
+    float* Vb = Vs + buf * kChunk * 32;
+    if (vec) {
+      for (int idx = threadIdx.x; idx < kChunk * (DP / 4); idx += 256) {
+        const int t = idx / (DP / 4), d = (idx % (DP / 4)) * 4;
+        const bool ok = d < a.dim;
+        cp_async16(Kb + t * LD + d, ok ? a.k + (row0 + t) * a.ldk + (int64_t) h * a.dim + d : a.k, ok);
+      }
+      {
+        const int t = threadIdx.x / 8, c = cg * 32 + (threadIdx.x % 8) * 4;
+        const bool ok = c < a.vdim;
+        cp_async16(Vb + t * 32 + (threadIdx.x % 8) * 4, ok ? a.v + (row0 + t) * a.ldv + (int64_t) h * a.vdim + c : a.v, ok);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < kChunk * DP; idx += 256) {
+        const int t = idx / DP, d = idx % DP;
+        Kb[t * LD + d] = d < a.dim ? a.k[(row0 + t) * a.ldk + (int64_t) h * a.dim + d] : 0.f;
+      }
+      for (int idx = threadIdx.x; idx < kChunk * 32; idx += 256) {
+        const int t = idx / 32, c = cg * 32 + idx % 32;
+        Vb[idx] = c < a.vdim ? a.v[(row0 + t) * a.ldv + (int64_t) h * a.vdim + c] : 0.f;
+      }
+    }
+    cp_async_commit();
+  };
+
+  load_chunk(0, 0);
+  int buf = 0;
+  for (int c0 = 0; c0 < len; c0 += kChunk, buf ^= 1) {
+    const int64_t row0 = start + c0;
+    const float* Kb = Ks + buf * kChunk * LD;
+    const float* Vb = Vs + buf * kChunk * 32;
+    cp_async_wait_all();
+    __syncthreads();
+    if (c0 + kChunk < len) load_chunk(c0 + kChunk, buf ^ 1);
+    if (warp == 0) {
+      float la = fixed_la, lb = 0.f;
+      if (a.log_ab) { la = a.log_ab[2 * ((row0 + lane) * a.heads + h)]; lb = a.log_ab[2 * ((row0 + lane) * a.heads + h) + 1]; }
+      float L = la;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float p = __shfl_up_sync(0xffffffffu, L, o);
+        if (lane >= o) L += p;
+      }
+      const float Ltot = __shfl_sync(0xffffffffu, L, 31);
+      wS[lane] = expf(Ltot - L + lb);
+      if (lane == 0) { dec_s[0] = expf(Ltot); dec_s[1] = Ltot; }
+    }
+    __syncthreads();
+    const float dec = dec_s[0];
+    Lsum += dec_s[1];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) s[i] *= dec;
+    for (int sk = 0; sk < kChunk; ++sk) {
+      const float wv = wS[sk] * (ones_here ? 1.f : Vb[sk * 32 + lane]);
+      const float* kr = Kb + sk * LD + warp * DPT;
+      if constexpr (DPT % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < DPT; i += 4) {
+          const float4 kv = *reinterpret_cast<const float4*>(kr + i);
+          s[i] = fmaf(wv, kv.x, s[i]); s[i + 1] = fmaf(wv, kv.y, s[i + 1]); s[i + 2] = fmaf(wv, kv.z, s[i + 2]); s[i + 3] = fmaf(wv, kv.w, s[i + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < DPT; i += 2) {
+          const float2 kv = *reinterpret_cast<const float2*>(kr + i);
+          s[i] = fmaf(wv, kv.x, s[i]); s[i + 1] = fmaf(wv, kv.y, s[i + 1]);
+        }
+      }
+    }
+  }
+  if (col_ok) {
+    float* dst = a.ws + (((int64_t) e * a.max_segs + sg + 1) * a.heads + h) * a.vcols * a.dim + (int64_t) col * a.dim;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int d = warp * DPT + i;
+      if (d < a.dim) dst[d] = s[i];
+    }
+  }
+  if (cg == 0 && threadIdx.x == 0) a.lseg[((int64_t) e * a.max_segs + sg) * a.heads + h] = Lsum;
+}
+
+// ws[sg + 1] (segment sg's own end state) -> the state segment sg + 1 starts from: run <- exp(sum of ln a over sg) * run + own, in
+// order; ws[0] <- the state the sequence brings
+__global__ void decay_segment_carry_kernel(ScanArgs a) {
+  const int e = blockIdx.y;
+  const int64_t per = (int64_t) a.heads * a.vcols * a.dim;
+  const int64_t idx = blockIdx.x * (int64_t) blockDim.x + threadIdx.x;
+  if (idx >= per) return;
+  const int len = a.seq_len[e];
+  const int nseg = (len + a.seg_rows - 1) / a.seg_rows;
+  if (nseg <= 1) return;
+  const int h = (int) (idx / ((int64_t) a.vcols * a.dim));
+  float run = a.seq_past[e] > 0 ? a.state[(int64_t) a.seq_slot[e] * a.state_stride + idx] : 0.f;
+  a.ws[(int64_t) e * a.max_segs * per + idx] = run;
+  for (int sg = 0; sg + 1 < nseg; ++sg) {
+    float* p = a.ws + ((int64_t) e * a.max_segs + sg + 1) * per + idx;
+    run = fmaf(expf(a.lseg[((int64_t) e * a.max_segs + sg) * a.heads + h]), run, *p);
+    *p = run;
   }
 }
 
@@ -380,6 +523,20 @@ int launch_chunk(float* out, const ScanArgs& a, int seqs, cudaStream_t st) {
   // cp.async moves 16 bytes: every row of q, k, v and every head and column group inside it must start on such a boundary
   const int vec = a.dim % 4 == 0 && a.vdim % 4 == 0 && a.ldq % 4 == 0 && a.ldk % 4 == 0 && a.ldv % 4 == 0 &&
                   (uintptr_t) a.q % 16 == 0 && (uintptr_t) a.k % 16 == 0 && (uintptr_t) a.v % 16 == 0;
+  if (a.ws) {
+    constexpr size_t smem_a = ((size_t) 2 * kChunk * LD + 2 * kChunk * 32 + kChunk + 2) * sizeof(float);
+    static bool raised_a = false;
+    if (!raised_a && smem_a > 48 * 1024) {
+      TB_CHECK_CUDA(cudaFuncSetAttribute(decay_segment_state_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_a));
+      raised_a = true;
+    }
+    dim3 grid((a.vcols + 31) / 32, a.heads, seqs * a.max_segs);
+    decay_segment_state_kernel<DPT><<<grid, 256, smem_a, st>>>(a, vec);
+    const int64_t per = (int64_t) a.heads * a.vcols * a.dim;
+    decay_segment_carry_kernel<<<dim3((unsigned) ((per + 255) / 256), seqs), 256, 0, st>>>(a);
+    decay_scan_chunk_kernel<DPT><<<grid, 256, smem, st>>>(out, a, vec);
+    return 0;
+  }
   dim3 grid((a.vcols + 31) / 32, a.heads, seqs);
   decay_scan_chunk_kernel<DPT><<<grid, 256, smem, st>>>(out, a, vec);
   return 0;
@@ -462,17 +619,34 @@ extern "C" int tb_mlstm_gates(float* log_ab, float* m_out, const float* proj, in
 static int g_decay_scan_mode = 0;
 extern "C" int tb_decay_scan_set_mode(int mode) { g_decay_scan_mode = mode; return 0; }
 
+// Segments a long portion is cut into so that the chip is filled: enough CTAs for two per SM, at least two chunks of 32 rows per
+// segment, at most 16 (the workspace holds a state per segment).  1: the portion runs as one.
+extern "C" int tb_decay_scan_segments(int seqs, int heads, int vcols, int max_len) {
+  if (seqs <= 0 || heads <= 0 || vcols <= 0 || max_len <= 0 || g_decay_scan_mode == 2) return 1;
+  const int64_t base = (int64_t) ((vcols + 31) / 32) * heads * seqs;
+  int64_t segs = (2 * 148 + base - 1) / base;
+  segs = std::min<int64_t>(segs, std::min(16, max_len / 64));
+  return segs < 2 ? 1 : (int) segs;
+}
+
 extern "C" int tb_decay_attention_scan(float* out, const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
                                        const float* log_ab, const float* head_decay, float* state, int64_t state_stride,
                                        const int* seq_start, const int* seq_len, const int* seq_past, const int* seq_slot, int rows,
                                        int seqs, int heads, int dim, int vdim, int ones_col, float q_scale, int max_len,
-                                       tb_stream_t stream) {
+                                       float* workspace, int segments, tb_stream_t stream) {
   if (!out || !q || !k || !v || !state || !seq_start || !seq_len || !seq_past || !seq_slot || (!log_ab && !head_decay)) return -1;
   if (heads <= 0 || dim <= 0 || dim > 1024 || vdim <= 0 || rows < 0 || seqs < 0 || seqs > 65535 || heads > 65535) return -1;
   if (rows == 0 || seqs == 0) return 0;
   ScanArgs a{q, k, v, ldq, ldk, ldv, log_ab, head_decay, state, state_stride, seq_start, seq_len, seq_past, seq_slot, heads, dim, vdim,
-             vdim + (ones_col ? 1 : 0), q_scale};
+             vdim + (ones_col ? 1 : 0), q_scale, nullptr, nullptr, 1, 0};
   cudaStream_t st = (cudaStream_t) stream;
+  if (segments > 1 && workspace && max_len >= 64 * segments) {
+    // workspace: [seqs, segments, heads, vcols, dim] states, then [seqs, segments, heads] sums of ln a
+    a.max_segs = segments;
+    a.seg_rows = (((max_len + segments - 1) / segments + kChunk - 1) / kChunk) * kChunk;
+    a.ws = workspace;
+    a.lseg = workspace + (int64_t) seqs * segments * heads * a.vcols * dim;
+  }
   if (g_decay_scan_mode != 1 && max_len >= 4 && dim <= 256) {
     const int dpt = (dim + 7) / 8;
     int rc;

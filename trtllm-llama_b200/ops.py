@@ -783,6 +783,7 @@ def mlstm_gates(proj, col_i, col_f, bias_i, bias_f, cap, m_state, batch, heads):
 
 
 FORCE_ROW_SCAN = False      # A/B: the decayed linear attention row by row also for prompt portions
+FORCE_ONE_SEGMENT = False   # A/B: ... and long portions as one segment
 
 
 def decay_attention_scan(q, k, v, state, batch, heads, dim, vdim, log_ab=None, head_decay=None, ones_col=False, q_scale=1.0):
@@ -796,10 +797,15 @@ def decay_attention_scan(q, k, v, state, batch, heads, dim, vdim, log_ab=None, h
             raise ValueError("decay_attention_scan: fp32 rows with unit inner stride")
     vcols = vdim + (1 if ones_col else 0)
     out = torch.empty((q.shape[0], heads, vcols), dtype=torch.float32, device=q.device)
+    # long portions of few sequences: segments side by side, their states carried in order (a state per segment in the workspace)
+    segs = 1 if FORCE_ROW_SCAN or FORCE_ONE_SEGMENT else _rl.tb_decay_scan_segments(batch.num_seqs, heads, vcols, batch.max_len)
+    ws = None
+    if segs > 1:
+        ws = torch.empty((batch.num_seqs * segs * (heads * vcols * dim + heads),), dtype=torch.float32, device=q.device)
     check(_rl.tb_decay_attention_scan(_p(out), _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(log_ab), _p(head_decay),
                                       _p(state), state.stride(0), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
                                       _p(batch.seq_slot), q.shape[0], batch.num_seqs, heads, dim, vdim, int(bool(ones_col)), float(q_scale),
-                                      1 if FORCE_ROW_SCAN else batch.max_len, _stream()), "tb_decay_attention_scan")
+                                      1 if FORCE_ROW_SCAN else batch.max_len, _p(ws), segs, _stream()), "tb_decay_attention_scan")
     return out
 
 
@@ -835,7 +841,11 @@ def residual_sandwich_layernorm_rows(x, y, w_post, b_post, out_scale, eps, w_pre
     return h
 
 
-SIDE_FUSED_MAX_ROWS = 8     # up to this many rows the per-layer token input is one kernel; above, its products run as projections
+# The per-layer token input is ONE kernel (a CTA per row does both products) while the step has few rows and the two weight
+# matrices are small — launch-bound steps of small models; otherwise its products run as projections (tensor cores / streaming
+# kernels that spread the weights over the chip) and the kernel only finishes (norm, residual step, next norm).
+SIDE_FUSED_MAX_ROWS = 8
+SIDE_FUSED_MAX_WEIGHTS = 16384
 
 
 def token_side_input(x, side_embed, e_off, ids, w_gate, w_proj, norm_w, eps, w_pre=None, b_pre=None, pre_rms=False,
@@ -852,8 +862,8 @@ def token_side_input(x, side_embed, e_off, ids, w_gate, w_proj, norm_w, eps, w_p
             raise TypeError("token_side_input: tensors of one storage type")
     h = torch.empty(x.shape, dtype=out_dtype, device=x.device) if w_pre is not None else None
     y = None
-    if x.shape[0] > SIDE_FUSED_MAX_ROWS:
-        # prompt-sized steps: the two products as projections (tensor cores for bf16), the kernel below finishes
+    if x.shape[0] > SIDE_FUSED_MAX_ROWS or sd * width > SIDE_FUSED_MAX_WEIGHTS:
+        # the two products as projections, the kernel below finishes
         z = linear(x, w_gate, out_dtype=torch.float32)
         g = torch.empty((x.shape[0], sd), dtype=w_gate.dtype, device=x.device)
         check(_rl.tb_side_gate_mul(_p(g), _dt(g), _p(z), z.stride(0), _p(side_embed), _dt(side_embed), side_embed.stride(0), int(e_off),
