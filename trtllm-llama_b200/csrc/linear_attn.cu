@@ -619,12 +619,13 @@ extern "C" int tb_mlstm_gates(float* log_ab, float* m_out, const float* proj, in
 static int g_decay_scan_mode = 0;
 extern "C" int tb_decay_scan_set_mode(int mode) { g_decay_scan_mode = mode; return 0; }
 
-// Segments a long portion is cut into so that the chip is filled: enough CTAs for two per SM, at least two chunks of 32 rows per
-// segment, at most 16 (the workspace holds a state per segment).  1: the portion runs as one.
+// Segments a long portion is cut into so that the chip is filled: as many as still run as ONE wave of two CTAs per SM (a second,
+// partly filled wave would cost a whole segment's time), at least two chunks of 32 rows per segment, at most 16 (the workspace
+// holds a state per segment).  1: the portion runs as one.
 extern "C" int tb_decay_scan_segments(int seqs, int heads, int vcols, int max_len) {
   if (seqs <= 0 || heads <= 0 || vcols <= 0 || max_len <= 0 || g_decay_scan_mode == 2) return 1;
   const int64_t base = (int64_t) ((vcols + 31) / 32) * heads * seqs;
-  int64_t segs = (2 * 148 + base - 1) / base;
+  int64_t segs = (2 * kNumSMs) / base;
   segs = std::min<int64_t>(segs, std::min(16, max_len / 64));
   return segs < 2 ? 1 : (int) segs;
 }
