@@ -400,6 +400,22 @@ def test_experts_whose_score_weighs_their_input(dtype, n, top, tiles, monkeypatc
     assert (want[:8] - on_output[:8]).abs().max() > 0.05 * want[:8].abs().max() or dtype == torch.bfloat16
 
 
+@pytest.mark.parametrize("top", [1, 2, 4])
+def test_router_choice_where_the_sigmoid_saturates(top):
+    """Logits of 17 and more all have the score 1 in fp32; the largest LOGITS are still the ones chosen (in their order), their weights
+    are the rounded scores, and small or negative logits are ranked as before."""
+    from trtllm_llama_b200 import ops
+    g = torch.Generator().manual_seed(top)
+    n, E = 37, 9
+    z = torch.stack([torch.randperm(E, generator=g).float() * 1.5 + 16.0 for _ in range(n)])
+    z[1::3] -= 24.0                                          # rows in the ordinary range, rows far below it
+    z[2::3] -= 60.0
+    ids, w = ops.moe_route(z.cuda(), None, top, 1, 1)
+    want = z.double().topk(top, dim=-1)
+    assert torch.equal(ids.cpu().long(), want.indices)
+    assert torch.allclose(w.cpu().double(), torch.sigmoid(want.values), rtol=3e-6, atol=1e-30)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n", [3, 50])
 def test_gated_gelu_feed_forward(dtype, n):

@@ -6,7 +6,8 @@
 //   moe_route_kernel    one warp per token: s = sigmoid(logit); choice = s + correction; experts form `groups` equal
 //                       groups of neighbours, a group scores the sum of its two largest choices, only the `keep` best
 //                       groups stay eligible; the `top` largest eligible choices are taken (ties: the lower index), and
-//                       their weights are the plain s, not renormalised.  All fp32.
+//                       their weights are the plain s, not renormalised.  All fp32.  With neither correction nor
+//                       groups the choice ranks the logits themselves (the same order, no saturation).
 //   moe_route_softmax_kernel  one warp per token: s = softmax over all experts, the `top` largest, weights s / sum(chosen) * scale.
 //   moe_plan_kernel     one CTA: pairs counted per expert, every expert's range padded to whole tiles of `tile` rows
 //                       (so a tile never mixes experts), tile -> expert table, and sorted slot -> pair index (-1 in the
@@ -50,10 +51,14 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(int* ids, f
   float* sig = choice + E;
   int* state = reinterpret_cast<int*>(sig + E);
   float* gscore = reinterpret_cast<float*>(state + E);
+  // without a correction or groups the order of the scores is the order of the logits: ranking by the logit keeps apart
+  // what the sigmoid rounds to one value in fp32 (above ~17 every score is 1)
+  const bool by_logit = !corr && !(groups > 1 && keep < groups);
   for (int e = lane; e < E; e += 32) {
-    const float s = 1.f / (1.f + expf(-logits[(int64_t) row * E + e]));
+    const float z = logits[(int64_t) row * E + e];
+    const float s = 1.f / (1.f + expf(-z));
     sig[e] = s;
-    choice[e] = s + (corr ? ld_w(corr, c_dtype, e) : 0.f);
+    choice[e] = by_logit ? z : s + (corr ? ld_w(corr, c_dtype, e) : 0.f);
     state[e] = 0;
   }
   __syncwarp();
